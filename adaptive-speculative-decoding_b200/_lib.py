@@ -56,6 +56,22 @@ class RivetarConfigC(ctypes.Structure):
                 ("page_size", ctypes.c_int), ("ring", ctypes.c_int), ("dtype", ctypes.c_int)]
 
 
+class MavipelLayerC(ctypes.Structure):
+    """mirror of ``asd_mavipel_layer_config``"""
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "type", "heads", "kv_heads", "dim", "vdim", "conv", "decay_rank", "gate_rank", "a_heads", "a_kv_heads", "a_dim",
+        "a_vdim", "rot_dims", "window", "r_heads", "r_dim", "r_decay_rank", "ff_kind", "ff", "experts", "top", "expert_ff",
+        "shared_ff")] + [(n, ctypes.c_float) for n in ("rot_base", "scale", "softcap", "left_scale", "right_scale")]
+
+
+class MavipelConfigC(ctypes.Structure):
+    """mirror of ``asd_mavipel_config``"""
+    _fields_ = [("width", ctypes.c_int), ("vocab", ctypes.c_int), ("n_layers", ctypes.c_int), ("eps", ctypes.c_float),
+                ("norm_groups", ctypes.c_int), ("loop_start", ctypes.c_int), ("loop_stop", ctypes.c_int),
+                ("loop_times", ctypes.c_int), ("max_tokens", ctypes.c_int), ("page_size", ctypes.c_int),
+                ("ring", ctypes.c_int), ("dtype", ctypes.c_int)]
+
+
 def library_path() -> str:
     return os.path.join(_HERE, "libasd_b200.so")
 
@@ -129,6 +145,16 @@ def lib() -> ctypes.CDLL:
         "asd_rivetar_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
         "asd_rivetar_profile_read": (i32, [vp, vp, vp, i32]),
         "asd_rivetar_device_error": (i32, [vp]),
+        "asd_mavipel_create": (vp, [vp, vp]),
+        "asd_mavipel_destroy": (None, [vp]),
+        "asd_mavipel_set_tensor": (i32, [vp, i32, c.c_char_p, vp]),
+        "asd_mavipel_cache_bytes": (sz, [vp, i32]),
+        "asd_mavipel_state_bytes": (sz, [vp, i32]),
+        "asd_mavipel_set_cache": (i32, [vp, vp, i32, vp, i32, i32, vp]),
+        "asd_mavipel_set_option": (i32, [vp, c.c_char_p, i32]),
+        "asd_mavipel_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
+        "asd_mavipel_profile_read": (i32, [vp, vp, vp, i32]),
+        "asd_mavipel_device_error": (i32, [vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name, None)

@@ -23,13 +23,17 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-li
 COMPONENTS = {
     "core": ["core.cu"],
     "linear": ["gemm.cu", "gemm_tc.cu"],
-    "blocks": ["linear_simt.cu", "linear_tc.cu", "latent_attention.cu"],
-    "mezilix": ["mezilix_engine.cu", "stream_ops.cu", "moe.cu"],
-    "rivetar": ["rivetar_engine.cu", "norm_ops.cu", "gla.cu", "window_attention.cu"],
+    "blocks": ["linear_simt.cu", "linear_tc.cu"],
+    "latent": ["latent_attention.cu"],
+    "rows": ["norm_ops.cu", "moe.cu"],          # row kernels and the expert router that several families share
+    "mezilix": ["mezilix_engine.cu", "stream_ops.cu"],
+    "rivetar": ["rivetar_engine.cu", "gla.cu", "window_attention.cu"],
+    "mavipel": ["mavipel_engine.cu", "delta_rule.cu", "talking_attention.cu"],
     "qwen": ["engine.cu", "layers.cu", "attention.cu", "attention_tc.cu", "forward_persist.cu"],
     "sampling": ["api.cu", "sampler.cu", "stop_rule.cu"],
 }
-REQUIRES = {"mezilix": ("linear", "blocks"), "rivetar": ("linear", "blocks"), "qwen": ("linear",)}
+REQUIRES = {"mezilix": ("linear", "blocks", "latent", "rows"), "rivetar": ("linear", "blocks", "latent", "rows"),
+            "mavipel": ("linear", "blocks", "rows"), "qwen": ("linear",)}
 
 
 def all_components():

@@ -144,6 +144,8 @@ struct MoeRouterInput {
     int w_f32;
     int D;
     float* logits_out;      // optional [M][E]
+    const float* bias = nullptr;   // optional [E], added to the logits
+    int renorm = 0;                // 1: the gates are divided by their sum (softmax over the chosen logits alone)
 };
 int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E, int top, int* expert_of, float* gate,
                      int* counters, int* group_off, int* sorted_tok, int* slot_of, cudaStream_t stream);
@@ -158,6 +160,9 @@ int launch_embed_scaled(const SeqIndex& ix, const void* embed, int wf32, float s
 //   x_out = x_in + (post_w ? y / rms(y) * (1 + post_w) : y) + bias          (each term optional)
 //   hn    = x_out / rms(x_out) * (1 + next_w)   in the engine's element type (if next_w)
 //   hn    = [x_out | cat[m]]                     rows of 2 D elements        (if cat: input of a pass-entry projection)
+// plain_w: the weights are taken as they are instead of 1 + w.  groups > 1: the norm before the next sublayer divides
+// each of `groups` equal consecutive parts of the row by its own root mean square.  top > 0: the sum also takes the
+// routed experts' results, gate[m][k] * expert_out[slot_of[m][k]] for k < top in this order (moe.cu).
 struct RowClose {
     const float* x_in = nullptr;    // [M][D]; with `rows`: row r reads x_in[rows[r]]
     const int* rows = nullptr;
@@ -171,8 +176,19 @@ struct RowClose {
     int hn_f32 = 0;
     float eps = 0.f;
     int M = 0, D = 0;
+    int plain_w = 0, groups = 1;
+    const float* expert_out = nullptr;  // [M * top][D] rows by slot
+    const int* slot_of = nullptr;       // [M][top]
+    const float* gate = nullptr;        // [M][top]
+    int top = 0;
 };
 int launch_row_close(const RowClose& c, cudaStream_t stream);
+// x[m] = embed[token] with each of `groups` equal consecutive parts divided by its root mean square, times w; fp32
+int launch_embed_normed(const SeqIndex& ix, const void* embed, int wf32, const float* w, int groups, float eps, float* x,
+                        int D, cudaStream_t stream);
+// Feed-forward activations over `rows` rows: out[r][f] = gelu_tanh(z[r][f]) with z rows of F floats, or (gated)
+// silu(z[r][f]) * z[r][F + f] with z rows of 2 F floats (gate half, then up half); out in the engine's element type
+int launch_ff_act(const float* z, void* out, int of32, long long rows, int F, int gated, cudaStream_t stream);
 // out[m][0 .. n) = in[m][0 .. n) / rms * w (plain weight; plus_one: 1 + w), rows ld_in / ld_out apart
 int launch_rms_rows(const float* in, long long ld_in, const float* w, int plus_one, float eps, void* out, int of32,
                     long long ld_out, int M, int n, cudaStream_t stream);
@@ -228,6 +244,89 @@ int launch_window_attention(const SeqIndex& ix, const int* cu_q, const int* seq_
                             int max_kv_len, const float* q, long long ldq, const WindowDims& d, const float* sink,
                             const float* freq_v, const PagedRows& cache, void* out, int of32, int tiled,
                             const AttnSplit& ws, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- delta_rule.cu
+// Channel functions of a low-rank projection: out[m][c] = post( w2[c] . inner(a[m]) + bias[c] ), fp32 throughout.
+enum { LRC_SIGMOID = 0, LRC_EXP_SOFTPLUS = 1, LRC_EXP_SIGMOID = 2 };
+struct LowRankChannels {
+    const float* w2 = nullptr;     // [n][low]
+    const float* bias = nullptr;   // [n] (optional)
+    int low = 0, n = 0;
+    int inner_tanh = 0;            // the inner vector passes tanh first
+    int post = LRC_SIGMOID;        // sigmoid(z) | exp(-exp(head_log_rate[c / per_head]) * softplus(z)) | exp(-rate * sigmoid(z))
+    const float* head_log_rate = nullptr;
+    int per_head = 0;
+    float rate = 1.f;
+};
+// a = fp32 rows of `low` floats lda apart; out fp32 [M][n]
+int launch_lowrank_channels(const float* a, long long lda, const LowRankChannels& p, float* out, int M, cudaStream_t stream);
+// Short causal convolution over time per channel, then silu: out[m][c] = silu(sum_j taps[c][j] in[pos - (n - 1 - j)][c]),
+// zeros before position 0.  in = fp32 rows ld apart (C used), out fp32 [M][C].  Inputs of earlier forwards come from
+// ring fp32 [slots][ring_n][C], entry p % ring_n = the input at position p (ring_n >= n - 1); launch_conv_commit stores
+// the last ring_n new positions of every sequence there and must follow the convolution.
+int launch_short_conv(const SeqIndex& ix, const float* in, long long ld, const float* taps, int n_taps, int C,
+                      const float* ring, int ring_n, float* out, cudaStream_t stream);
+int launch_conv_commit(const SeqIndex& ix, const int* cu_q, int nseq, const float* in, long long ld, int C, float* ring,
+                       int ring_n, cudaStream_t stream);
+// The vectors a position's recurrence step reads, rv fp32 [M][heads][4 or 5][dk] and sc fp32 [M][heads][4] (layout in
+// delta_rule.cu).  Gated rule (general = 0): q, k = fp32 rows ld apart holding kv_heads * dk values (head h reads key
+// head h / (heads / kv_heads)), made unit vectors (x / sqrt(sum x^2 + tiny)), q times q_scale; beta = raw rows (ld_beta
+// apart, one per head) that pass a sigmoid; decay fp32 [M][heads * dk].  Generalised rule (general = 1): q = the
+// read-out vectors, k = the keys, rate (raw, ld apart) + rate_bias [heads * dk] pass a sigmoid.
+struct DeltaPrep {
+    const float* q = nullptr;
+    const float* k = nullptr;
+    long long ld = 0;
+    const float* decay = nullptr;
+    const float* beta = nullptr;
+    long long ld_beta = 0;
+    const float* rate = nullptr;
+    const float* rate_bias = nullptr;
+    float* rv = nullptr;
+    float* sc = nullptr;
+    int heads = 0, kv_heads = 0, dk = 0, general = 0;
+    float q_scale = 1.f, tiny = 1e-6f;
+};
+int launch_delta_prep(const DeltaPrep& p, int M, cudaStream_t stream);
+// state fp32 [slots][ring][heads][dk][dv]; entry position % ring holds the state after that position.  A sequence whose
+// first new position is 0 starts from zero, any other from entry (position - 1) % ring; the last `ring` new positions
+// of a sequence store theirs.  v = fp32 rows ldv apart (heads * dv used); out fp32 [M][heads * dv].
+int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, const float* rv,
+                            const float* sc, int general, const float* v, long long ldv, int heads, int dk, int dv,
+                            float* state, int ring, float* out, cudaStream_t stream);
+// y[m][h][:] = o[m][h][:] / rms(o[m][h][:]) * w * gate[m][h][:] * scale, y = rows ldy apart in the engine's element
+// type.  w: [dv] shared by the heads or [heads * dv]; gate: fp32 rows ldg apart, taken as they are or through a sigmoid.
+struct HeadNormGate {
+    const float* gate = nullptr;
+    long long ldg = 0;
+    const float* w = nullptr;
+    int w_per_head = 0, gate_sigmoid = 0;
+    float eps = 0.f, scale = 1.f;
+};
+int launch_head_norm_gate(const float* o, const HeadNormGate& p, void* y, int of32, long long ldy, int M, int heads, int dv,
+                          cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- talking_attention.cu
+// Grouped-query softmax attention over a sliding window whose scores are capped (cap * tanh(s / cap)) and then mixed
+// across the heads, s'_h = sum_g talk[h][g] s_g, before a softmax with a sink per head in the denominator.
+// Cache row per position: [kv_heads * dk normed, rotated keys | kv_heads * dv values].
+struct TalkDims {
+    int heads, kv_heads, dk, dv;
+    int rot_dims;      // leading key/query coordinates that rotate in pairs (2 i, 2 i + 1)
+    int window;        // position i sees j <= i with i - j < window
+    float scale;
+    float softcap;     // 0: scores are not capped
+};
+// qkv fp32 rows (ld floats apart) = [heads * dk | kv_heads * dk | kv_heads * dv].  Adds the biases (fp32, same layout,
+// optional), RMS-norms every query and key head over dk (plain weights q_norm, k_norm [dk]; nullptr: none), rotates
+// them, leaves the queries in place and appends keys and values to the cache.  freq fp32 [rot_dims / 2].
+int launch_talk_post(const SeqIndex& ix, float* qkv, long long ld, const TalkDims& d, const float* bias, const float* q_norm,
+                     const float* k_norm, float eps, const float* freq, const PagedRows& cache, cudaStream_t stream);
+// out[m][h][:] (rows ldo apart, engine's element type) = out_scale * sum_j p[h][j] v[j]; talk fp32 [heads][heads]
+// (nullptr: no mixing), sink fp32 [heads] (nullptr: none).
+int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+                          const float* q, long long ldq, const TalkDims& d, const float* talk, const float* sink,
+                          const PagedRows& cache, void* out, int of32, long long ldo, float out_scale, cudaStream_t stream);
 
 int preload_blocks();
 

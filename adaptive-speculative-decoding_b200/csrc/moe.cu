@@ -1,5 +1,5 @@
 // Mixture-of-experts routing: fp32 softmax over all experts, the `top` largest probabilities kept as gates (as they
-// are, no renormalisation), then the (token, choice) pairs grouped by expert so that each expert's rows are contiguous
+// are, or divided by their sum, which is the softmax over the chosen logits alone), then the (token, choice) pairs grouped by expert so that each expert's rows are contiguous
 // for the grouped linear layers.  Which slot inside an expert's group a pair gets does not matter for the result: every
 // slot is computed on its own and a token's choices are summed in choice order by the layer close.
 #include <cuda_runtime.h>
@@ -18,7 +18,8 @@ namespace {
 // increasing d, then the fixed warp tree: the same for a token whatever else is in the batch), eight experts per pass
 // over the row.
 __global__ void moe_route_kernel(const float* logits, const void* x, int xf32, const void* wr, int wf32, int D, float* z_out,
-                                 int M, int E, int top, int* expert_of, float* gate, int* counts) {
+                                 int M, int E, int top, int* expert_of, float* gate, int* counts, const float* bias,
+                                 int renorm) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -40,8 +41,9 @@ __global__ void moe_route_kernel(const float* logits, const void* x, int xf32, c
             for (int j = 0; j < 8; ++j) {
                 const float v = warp_sum(acc[j]);
                 if (lane == 0 && e0 + j < E) {
-                    zs[e0 + j] = v;
-                    if (z_out) z_out[(long long)m * E + e0 + j] = v;
+                    const float zb = bias ? v + bias[e0 + j] : v;
+                    zs[e0 + j] = zb;
+                    if (z_out) z_out[(long long)m * E + e0 + j] = zb;
                 }
             }
         }
@@ -59,6 +61,7 @@ __global__ void moe_route_kernel(const float* logits, const void* x, int xf32, c
     }
     s = warp_sum(s);
     const float inv = 1.f / s;
+    float chosen = 0.f;
     __syncwarp();
     for (int k = 0; k < top; ++k) {
         float best = -1.f;
@@ -82,17 +85,23 @@ __global__ void moe_route_kernel(const float* logits, const void* x, int xf32, c
         if (lane == 0) {
             expert_of[(long long)m * top + k] = bi;
             gate[(long long)m * top + k] = best * inv;
+            chosen += best;
             atomicAdd(&counts[bi], 1);
             pr[bi] = -2.f;         // taken
         }
         __syncwarp();
+    }
+    if (renorm && lane == 0) {   // gates over the chosen alone: e^(z - max) / sum of the chosen e^(z - max)
+        const float r = 1.f / (chosen * inv);
+        for (int k = 0; k < top; ++k) gate[(long long)m * top + k] *= r;
     }
 }
 
 // Few tokens (M * top <= 4096): choice, group sizes, offsets and scatter in ONE CTA with shared-memory counters, so that a
 // decode step spends two launches on routing (logits, then this) instead of five.
 __global__ void __launch_bounds__(256) moe_route_small_kernel(const float* logits, int M, int E, int top, int* expert_of,
-                                                              float* gate, int* group_off, int* sorted_tok, int* slot_of) {
+                                                              float* gate, int* group_off, int* sorted_tok, int* slot_of,
+                                                              int renorm) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     int* cnt = reinterpret_cast<int*>(sm + (size_t)nw * E);     // [E] group sizes, then fill counters
@@ -113,6 +122,7 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(const float* logit
         }
         s = warp_sum(s);
         const float inv = 1.f / s;
+        float chosen = 0.f;
         __syncwarp();
         for (int k = 0; k < top; ++k) {
             float best = -1.f;
@@ -136,10 +146,15 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(const float* logit
             if (lane == 0) {
                 expert_of[(long long)m * top + k] = bi;
                 gate[(long long)m * top + k] = best * inv;
+                chosen += best;
                 atomicAdd(&cnt[bi], 1);
                 pr[bi] = -2.f;
             }
             __syncwarp();
+        }
+        if (renorm && lane == 0) {
+            const float r = 1.f / (chosen * inv);
+            for (int k = 0; k < top; ++k) gate[(long long)m * top + k] *= r;
         }
     }
     __syncthreads();
@@ -166,7 +181,7 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(const float* logit
 // router logits, one CTA per token: z[m][e] = sum_d x[m][d] * wr[e][d] in fp32.  Thread t sums d = t, t + 128, ... in
 // increasing order, then the fixed warp tree and the warps in index order: a token's logits do not depend on the batch.
 __global__ void __launch_bounds__(128) moe_logits_kernel(const void* x, int xf32, const void* wr, int wf32, int D, int E,
-                                                         float* z_out) {
+                                                         float* z_out, const float* bias) {
     __shared__ float red[4][8];
     const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int e0 = 0; e0 < E; e0 += 8) {
@@ -188,7 +203,8 @@ __global__ void __launch_bounds__(128) moe_logits_kernel(const void* x, int xf32
         __syncthreads();
         if (threadIdx.x < 8 && e0 + threadIdx.x < E)
             z_out[(long long)m * E + e0 + threadIdx.x] =
-                ((red[0][threadIdx.x] + red[1][threadIdx.x]) + red[2][threadIdx.x]) + red[3][threadIdx.x];
+                (((red[0][threadIdx.x] + red[1][threadIdx.x]) + red[2][threadIdx.x]) + red[3][threadIdx.x]) +
+                (bias ? bias[e0 + threadIdx.x] : 0.f);
     }
 }
 
@@ -222,24 +238,25 @@ int launch_moe_route(const float* logits, const MoeRouterInput* in, int M, int E
     if (E <= 0 || top <= 0 || top > E) return set_error("moe: need 0 < top <= experts (top %d, experts %d)", top, E);
     if ((size_t)E * 8 * sizeof(float) > 48 * 1024) return set_error("moe: more than 1536 experts");
     if (!logits && !in) return set_error("moe: neither logits nor router inputs");
+    const int renorm = in ? in->renorm : 0;
     if (in && in->logits_out && (long long)M * top <= 4096 && (size_t)(8 * E + 2 * E + 1) * 4 <= 48 * 1024) {
-        moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out);
+        moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out, in->bias);
         moe_route_small_kernel<<<1, 256, (size_t)(8 * E + 2 * E + 1) * sizeof(float), stream>>>(
-            in->logits_out, M, E, top, expert_of, gate, group_off, sorted_tok, slot_of);
+            in->logits_out, M, E, top, expert_of, gate, group_off, sorted_tok, slot_of, in->renorm);
         count_launch(2);
         ASD_CUDA(cudaGetLastError());
         return 0;
     }
     ASD_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * E, stream));
     if (in && in->logits_out) {          // a CTA per token for the logits: few tokens still spread over the GPU
-        moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out);
+        moe_logits_kernel<<<M, 128, 0, stream>>>(in->x, in->x_f32, in->w, in->w_f32, in->D, E, in->logits_out, in->bias);
         count_launch(1);
         logits = in->logits_out;
         in = nullptr;
     }
     moe_route_kernel<<<(M + 3) / 4, 128, (size_t)E * 8 * sizeof(float), stream>>>(
         logits, in ? in->x : nullptr, in ? in->x_f32 : 0, in ? in->w : nullptr, in ? in->w_f32 : 0, in ? in->D : 0,
-        nullptr, M, E, top, expert_of, gate, counters);
+        nullptr, M, E, top, expert_of, gate, counters, in ? in->bias : nullptr, renorm);
     moe_offsets_kernel<<<1, 32, 0, stream>>>(counters, group_off, E);
     const int n = M * top;
     moe_scatter_kernel<<<(n + 255) / 256, 256, 0, stream>>>(expert_of, n, top, E, group_off, counters, sorted_tok, slot_of);

@@ -10,7 +10,8 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import AsdError, MezilixConfigC, MezilixLayerC, ModelConfigC, RivetarConfigC, RivetarLayerC, check, lib
+from ._lib import (AsdError, MavipelConfigC, MavipelLayerC, MezilixConfigC, MezilixLayerC, ModelConfigC, RivetarConfigC,
+                   RivetarLayerC, check, lib)
 from .models.qwen2 import Qwen2Config, pack_layer, random_packed_layer
 from .ops import NUM_FEATURES
 
@@ -590,25 +591,17 @@ class RivetarEngine(_SlotOps, _BatchOps):
     everywhere).  Same ``forward`` interface as ``QwenEngine``, so ``SpecDecoder`` and ``Stage`` drive it unchanged."""
 
     TYPE_CODE = {"latent_attention": 0, "gla": 1, "attention": 2}
+    PREFIX = "rivetar"          # asd_<PREFIX>_* entry points of the library
 
-    def __init__(self, cfg, max_seqs: int, max_seq_len: int, max_tokens: int = 1024, page_size: int = 16,
-                 device="cuda", dtype=torch.bfloat16, ring: int = 1, num_pages: Optional[int] = None,
-                 dynamic_pages: bool = False, shuffle_pages: bool = True):
-        if not torch.cuda.is_available():
-            raise AsdError("RivetarEngine needs a CUDA device (there is no CPU fallback)")
-        if dtype not in (torch.bfloat16, torch.float32):
-            raise AsdError(f"RivetarEngine runs in bfloat16 or float32, not {dtype}")
-        dev = torch.device(device)
-        if dev.index is None:
-            dev = torch.device("cuda", torch.cuda.current_device())
-        self.cfg, self.device, self.dtype = cfg, dev, dtype
-        self.tp_rank, self.tp_size = 0, 1
-        self.max_seqs, self.max_seq_len, self.max_tokens, self.page_size = max_seqs, max_seq_len, max_tokens, page_size
-        self.ring = int(ring)
+    def _fn(self, name: str):
+        return getattr(lib(), f"asd_{self.PREFIX}_{name}")
+
+    def _c_config(self, cfg, max_tokens: int, page_size: int, dtype):
+        """(configuration struct, layer struct array) for ``asd_<PREFIX>_create``"""
         loop = cfg.loop or (0, 0, 0)
-        self.c = RivetarConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.embed_scale,
-                                cfg.logit_softcap, loop[0], loop[1], loop[2], max_tokens, page_size, self.ring,
-                                1 if dtype == torch.float32 else 0)
+        c = RivetarConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.embed_scale,
+                           cfg.logit_softcap, loop[0], loop[1], loop[2], max_tokens, page_size, self.ring,
+                           1 if dtype == torch.float32 else 0)
         arr = (RivetarLayerC * max(1, cfg.num_hidden_layers))()
         for i, l in enumerate(cfg.layers):
             if l.type == "gla" and l.decay_rank <= 0:
@@ -617,28 +610,45 @@ class RivetarEngine(_SlotOps, _BatchOps):
             arr[i] = RivetarLayerC(self.TYPE_CODE[l.type], l.heads, l.kv_heads, l.dim, l.vdim, l.rot_dim, l.kv_rank,
                                    l.q_rank, l.decay_rank, l.rot_dims, 1 if l.rot_layout == "interleaved" else 0,
                                    min(l.window, 1 << 30), l.keep_first, l.rot_base, l.scale, l.tau, l.ff)
+        return c, arr
+
+    def __init__(self, cfg, max_seqs: int, max_seq_len: int, max_tokens: int = 1024, page_size: int = 16,
+                 device="cuda", dtype=torch.bfloat16, ring: int = 1, num_pages: Optional[int] = None,
+                 dynamic_pages: bool = False, shuffle_pages: bool = True):
+        if not torch.cuda.is_available():
+            raise AsdError(f"{type(self).__name__} needs a CUDA device (there is no CPU fallback)")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise AsdError(f"{type(self).__name__} runs in bfloat16 or float32, not {dtype}")
+        dev = torch.device(device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.cfg, self.device, self.dtype = cfg, dev, dtype
+        self.tp_rank, self.tp_size = 0, 1
+        self.max_seqs, self.max_seq_len, self.max_tokens, self.page_size = max_seqs, max_seq_len, max_tokens, page_size
+        self.ring = int(ring)
+        self.c, arr = self._c_config(cfg, max_tokens, page_size, dtype)
         self._lock = threading.Lock()
         with torch.cuda.device(self.device):
-            self.h = lib().asd_rivetar_create(ctypes.byref(self.c), arr)
+            self.h = self._fn("create")(ctypes.byref(self.c), arr)
         if not self.h:
-            check(-1, "asd_rivetar_create")
+            check(-1, f"asd_{self.PREFIX}_create")
         self.n_runs = len(cfg.runs())
         self.max_pages = (max_seq_len + page_size - 1) // page_size
         self.pages = PageTable(max_seqs, self.max_pages, page_size, self.device, num_pages=num_pages,
                                dynamic=dynamic_pages, shuffle=shuffle_pages)
         self.num_pages = self.pages.num_pages
-        self.cache_pool = torch.zeros(max(lib().asd_rivetar_cache_bytes(self.h, self.num_pages), 16), dtype=torch.uint8,
+        self.cache_pool = torch.zeros(max(self._fn("cache_bytes")(self.h, self.num_pages), 16), dtype=torch.uint8,
                                       device=self.device)
-        self.state = torch.zeros(max(lib().asd_rivetar_state_bytes(self.h, max_seqs) // 4, 4), dtype=torch.float32,
+        self.state = torch.zeros(max(self._fn("state_bytes")(self.h, max_seqs) // 4, 4), dtype=torch.float32,
                                  device=self.device)
-        check(lib().asd_rivetar_set_cache(self.h, self.cache_pool.data_ptr(), self.num_pages, self.pages.table.data_ptr(),
-                                          max_seqs, self.max_pages, self.state.data_ptr()), "asd_rivetar_set_cache")
+        check(self._fn("set_cache")(self.h, self.cache_pool.data_ptr(), self.num_pages, self.pages.table.data_ptr(),
+                                    max_seqs, self.max_pages, self.state.data_ptr()), f"asd_{self.PREFIX}_set_cache")
         self._weights = {}
         self._index_cache = {}
 
     def close(self):
         if getattr(self, "h", None):
-            lib().asd_rivetar_destroy(self.h)
+            self._fn("destroy")(self.h)
             self.h = None
 
     def __del__(self):
@@ -650,27 +660,31 @@ class RivetarEngine(_SlotOps, _BatchOps):
     def max_qlen(self) -> int:
         return self.max_tokens          # every mixer's kernels tile any number of new positions
 
+    @staticmethod
+    def _family():
+        """module with ``pack`` and ``random_weights`` of this engine's family"""
+        from .models import rivetar
+        return rivetar
+
     # ------------------------------------------------------------------ weights
     def load_weights(self, w: Dict[str, torch.Tensor]):
         """state dict with the checkpoint's tensor names (any device, any float type) -> engine buffers"""
-        from .models.rivetar import pack
         try:
-            packed = pack(w, self.cfg, self.device, self.dtype)
+            packed = self._family().pack(w, self.cfg, self.device, self.dtype)
         except (KeyError, ValueError) as e:
             raise AsdError(str(e)) from e
         for (layer, name), t in packed.items():
-            check(lib().asd_rivetar_set_tensor(self.h, layer, name.encode(), t.data_ptr()), "asd_rivetar_set_tensor")
+            check(self._fn("set_tensor")(self.h, layer, name.encode(), t.data_ptr()), f"asd_{self.PREFIX}_set_tensor")
         self._weights = packed
         return self
 
     load_hf_weights = load_weights
 
     def load_random(self, seed: int, std: float = 0.02):
-        from .models.rivetar import random_weights
-        return self.load_weights(random_weights(self.cfg, seed, device=self.device))
+        return self.load_weights(self._family().random_weights(self.cfg, seed, device=self.device))
 
     def set_option(self, name: str, value: int):
-        check(lib().asd_rivetar_set_option(self.h, name.encode(), int(value)), "asd_rivetar_set_option")
+        check(self._fn("set_option")(self.h, name.encode(), int(value)), f"asd_{self.PREFIX}_set_option")
 
     PROFILE_CLASSES = ("dense", "head_products", "latent_attention", "window_attention", "recurrence", "activation",
                        "glue", "lm_head")
@@ -679,12 +693,12 @@ class RivetarEngine(_SlotOps, _BatchOps):
         """(ms, launches) per kernel class since the last read; needs set_option('profile', 1)."""
         n = len(self.PROFILE_CLASSES)
         ms, cnt = (ctypes.c_float * n)(), (ctypes.c_int * n)()
-        check(lib().asd_rivetar_profile_read(self.h, ms, cnt, n), "asd_rivetar_profile_read")
+        check(self._fn("profile_read")(self.h, ms, cnt, n), f"asd_{self.PREFIX}_profile_read")
         return {c: (ms[i], cnt[i]) for i, c in enumerate(self.PROFILE_CLASSES)}
 
     def check_device(self) -> None:
         """raises if a kernel of this engine gave up a bounded wait (synchronises)"""
-        check(lib().asd_rivetar_device_error(self.h), "asd_rivetar_device_error")
+        check(self._fn("device_error")(self.h), f"asd_{self.PREFIX}_device_error")
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens, positions, token_slot, cu_q, seq_slot, max_qlen: int, max_kv_len: int,
@@ -702,15 +716,51 @@ class RivetarEngine(_SlotOps, _BatchOps):
         streams = (torch.empty(self.n_runs, M, self.cfg.width, dtype=torch.float32, device=self.device)
                    if layer_out else None)
         with self._lock, torch.cuda.device(self.device):
-            rc = lib().asd_rivetar_forward(
+            rc = self._fn("forward")(
                 self.h, tokens.data_ptr(), positions.data_ptr(), token_slot.data_ptr(), M, cu_q.data_ptr(),
                 seq_slot.data_ptr(), nseq, max_qlen, max_kv_len,
                 None if logit_rows is None else logit_rows.data_ptr(), n_rows,
                 None if not n_rows else logits_out.data_ptr(), logits_ld,
                 None if streams is None else streams.data_ptr(), _stream())
-        check(rc, "asd_rivetar_forward")
+        check(rc, f"asd_{self.PREFIX}_forward")
         res = logits_out if n_rows else None
         return (res, streams) if layer_out else res
+
+
+class MavipelEngine(RivetarEngine):
+    """One Mavipel-family model on one GPU: wraps an ``asd_mavipel_engine_t`` handle.  Same ownership as
+    ``RivetarEngine``: per layer EXECUTION the paged key/value cache of a parallel layer's window attention
+    (``PageTable``) and, in one fp32 buffer, the carried inputs of the short convolutions and the recurrent states of the
+    delta rules, [slot][ring][heads][dim][vdim]; entry position % ring is the state after that position, and a forward
+    that starts a slot at position 0 starts from zero, so reused slots carry nothing over.  Same ``forward`` interface
+    as ``QwenEngine``, so ``SpecDecoder``, ``Stage`` and the trace runner drive it unchanged."""
+
+    TYPE_CODE = {"channel_delta": 0, "parallel": 1}
+    FF_CODE = {None: 0, "dense": 1, "moe": 2}
+    PREFIX = "mavipel"
+    PROFILE_CLASSES = ("dense", "window_attention", "recurrence", "experts", "router", "activation", "glue", "lm_head")
+
+    @staticmethod
+    def _family():
+        from .models import mavipel
+        return mavipel
+
+    def _c_config(self, cfg, max_tokens: int, page_size: int, dtype):
+        loop = cfg.loop or (0, 0, 0)
+        c = MavipelConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.norm_groups, loop[0], loop[1],
+                           loop[2], max_tokens, page_size, self.ring, 1 if dtype == torch.float32 else 0)
+        arr = (MavipelLayerC * max(1, cfg.num_hidden_layers))()
+        for i, l in enumerate(cfg.layers):
+            ranks = (l.decay_rank, l.gate_rank) if l.type == "channel_delta" else (l.r_decay_rank,)
+            if min(ranks) <= 0:
+                raise AsdError(f"layer {i}: the inner size of a two-matrix projection is unknown (a checkpoint's tensor "
+                               "shapes give it: MavipelConfig.with_shapes)")
+            arr[i] = MavipelLayerC(self.TYPE_CODE[l.type], l.heads, l.kv_heads, l.dim, l.vdim, l.conv, l.decay_rank,
+                                   l.gate_rank, l.a_heads, l.a_kv_heads, l.a_dim, l.a_vdim, l.rot_dims,
+                                   min(l.window, 1 << 30), l.r_heads, l.r_dim, l.r_decay_rank, self.FF_CODE[l.ff_kind], l.ff,
+                                   l.experts, l.top, l.expert_ff, l.shared_ff, l.rot_base, l.scale, l.softcap,
+                                   l.left_scale, l.right_scale)
+        return c, arr
 
 
 class TPQwenEngine(_BatchOps):

@@ -389,6 +389,89 @@ ASD_API int asd_rivetar_forward(asd_rivetar_engine_t* e, const int32_t* tokens, 
 ASD_API int asd_rivetar_profile_read(asd_rivetar_engine_t* e, float* ms_by_class, int* launches_by_class, int nclass);
 ASD_API int asd_rivetar_device_error(asd_rivetar_engine_t* e);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Mavipel family engine (mavipel_engine.cu).  x = group_norm(embed[token]) * embed_norm; every layer is pre-normed,
+ * x <- x + mixer(norm1(x)), x <- x + ff(norm2(x)); logits = head . final_norm(x).  Every norm splits its row into
+ * norm_groups equal consecutive parts, divides each by its root mean square (eps inside the root) and multiplies by a
+ * plain weight.  A layer's mixer is
+ *   type 0  gated delta rule: q, k (kv_heads x dim) and v (heads x vdim) pass a short causal convolution over time
+ *           (`conv` taps per channel) and silu; q and k become unit vectors per head, q times dim^(-1/2); a write
+ *           strength beta = sigmoid per head; a decay per head and key channel exp(-exp(a_log[head]) softplus(.)) from
+ *           a two-matrix projection of inner size decay_rank; per head S <- diag(g) S, u = beta (v - S^T k),
+ *           S <- S + k u^T, o = S^T q; o / rms(o) * out_norm[vdim] * sigmoid(two-matrix projection of inner size
+ *           gate_rank), then the output projection.
+ *   type 1  two mixers on the same input, left_scale * left + right_scale * right.  Left: grouped-query attention
+ *           (a_heads, a_kv_heads, a_dim, a_vdim) with biased projections, RMS norm of every query / key head (weights
+ *           [a_dim]), rotation of the leading rot_dims coordinates in pairs (2i, 2i + 1) by position * rot_base^(-2i /
+ *           rot_dims), scores * scale, capped by softcap * tanh(. / softcap) (softcap 0: not capped), mixed across the
+ *           heads by talk [a_heads][a_heads], a sliding window (i sees j <= i with i - j < window) and a softmax whose
+ *           denominator also holds exp(sink[head]).  Right: generalised delta rule over r_heads heads of r_dim: decay
+ *           w = exp(-e^(-1/2) sigmoid(W2 tanh(W1 h) + b)) (inner size r_decay_rank), removal rate a = sigmoid(. + bias),
+ *           n = unit key; S <- diag(w) S - (a * n)(n^T S) + k v^T (both terms read the old state), o = S^T r;
+ *           o / rms(o) per head * out_norm[r_heads * r_dim] * sigmoid(gate projection).
+ * ff_kind 0: none; 1: W_down gelu_tanh(W_up h); 2: `experts` gated experts W_down (silu(W_gate h) * W_up h) of which
+ * every token takes the `top` with the largest router logits (fp32, biased), weighted by the softmax over those logits
+ * alone, plus a shared expert of size shared_ff for every token (0: none).
+ * Layers loop_start .. loop_stop - 1 run loop_times times with the same weights (0: no repeated span); every execution
+ * ("run") has its own cache and state, and loop_step[pass] is added to x before a pass's first layer.
+ *
+ * dtype as for the Rivetar engine.  Paged pool: per run of a type 1 layer [num_pages][page_size][a_kv_heads * (a_dim +
+ * a_vdim)], keys then values, runs back to back.  State (caller allocated, fp32), per run: the convolution's carried
+ * inputs [max_seqs][conv - 1 + ring - 1][channels] (type 0), then the recurrent state [max_seqs][ring][heads][dim][vdim]
+ * (type 1: [r_heads][r_dim][r_dim]); entry position % ring holds the state AFTER that position, so a caller may re-feed
+ * any of the last `ring` positions; a run that starts at position 0 starts from zero.
+ */
+typedef struct asd_mavipel_layer_config {
+    int type;                                              /* 0 gated delta rule, 1 attention + generalised delta rule */
+    int heads, kv_heads, dim, vdim, conv, decay_rank, gate_rank;            /* type 0 */
+    int a_heads, a_kv_heads, a_dim, a_vdim, rot_dims, window;               /* type 1, left */
+    int r_heads, r_dim, r_decay_rank;                                       /* type 1, right */
+    int ff_kind, ff, experts, top, expert_ff, shared_ff;
+    float rot_base, scale, softcap, left_scale, right_scale;
+} asd_mavipel_layer_config;
+typedef struct asd_mavipel_config {
+    int width, vocab, n_layers;
+    float eps;
+    int norm_groups;
+    int loop_start, loop_stop, loop_times;
+    int max_tokens, page_size, ring, dtype;
+} asd_mavipel_config;
+typedef struct asd_mavipel_engine asd_mavipel_engine_t;
+
+ASD_API asd_mavipel_engine_t* asd_mavipel_create(const asd_mavipel_config* cfg, const asd_mavipel_layer_config* layers);
+ASD_API void asd_mavipel_destroy(asd_mavipel_engine_t* e);
+/* Weights by name; matrices row-major [out, in] in the engine's dtype, vectors and everything marked fp32 always fp32.
+ * layer -1: "embed" [vocab, width], "embed_norm" [width], "final_norm" [width], "head" [vocab, width], "loop_step"
+ * [times, width].  Every layer: "norm1" (and "norm2" when ff_kind > 0), "w_o" = the output projections side by side
+ * [width, columns], "w_in" = the matrices that read the mixer input stacked by rows:
+ *   type 0: [q | k | v | beta | decay-in | gate-in]; also "conv_w" fp32 [q, k, v channels][conv], "a_log" [heads],
+ *           "w_decay" fp32 [heads * dim, decay_rank], "b_decay" [heads * dim], "w_gate" fp32 [heads * vdim, gate_rank],
+ *           "out_norm" [vdim];
+ *   type 1: [left q | k | v | right r | k | v | gate | rate | decay-in]; also "in_bias" [left q | k | v], "q_norm",
+ *           "k_norm" [a_dim], "talk" fp32 [a_heads, a_heads], "sink" [a_heads], "w_decay" fp32 [r_heads * r_dim,
+ *           r_decay_rank], "b_decay", "rate_bias", "out_norm" [r_heads * r_dim].
+ * ff_kind 1: "w_up" [ff, width], "w_down" [width, ff].  ff_kind 2: "router" fp32 [experts, width], "router_b"
+ * [experts], "w_gu" [experts][2 expert_ff, width] (gate rows, then up rows), "w_edown" [experts][width, expert_ff],
+ * and with a shared expert "w_sgu" [2 shared_ff, width], "w_sdown" [width, shared_ff]. */
+ASD_API int asd_mavipel_set_tensor(asd_mavipel_engine_t* e, int layer, const char* name, const void* data);
+ASD_API size_t asd_mavipel_cache_bytes(const asd_mavipel_engine_t* e, int num_pages);
+ASD_API size_t asd_mavipel_state_bytes(const asd_mavipel_engine_t* e, int max_seqs);
+ASD_API int asd_mavipel_set_cache(asd_mavipel_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
+                                  int max_seqs, int max_pages_per_seq, float* state);
+/* options: "tc_linear", "tc_min_rows" as for the Mezilix engine; "profile" */
+ASD_API int asd_mavipel_set_option(asd_mavipel_engine_t* e, const char* name, int value);
+/* Same arguments as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
+ * stream that leaves every layer execution. */
+ASD_API int asd_mavipel_forward(asd_mavipel_engine_t* e, const int32_t* tokens, const int32_t* positions,
+                                const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
+                                int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows,
+                                float* logits_out, long long logits_ld, float* layer_out, void* stream);
+/* ms and launches by kernel class since the last read (nclass >= 8): 0 dense projections, 1 window attention,
+ * 2 recurrences, 3 expert layers, 4 router, 5 feed-forward activations, 6 norms / convolution / channel functions /
+ * cache append, 7 output head */
+ASD_API int asd_mavipel_profile_read(asd_mavipel_engine_t* e, float* ms_by_class, int* launches_by_class, int nclass);
+ASD_API int asd_mavipel_device_error(asd_mavipel_engine_t* e);
+
 #ifdef __cplusplus
 }
 #endif
