@@ -72,7 +72,8 @@ def rotate_interleaved(x, positions, dims: int, base: float):
 def gated_delta_mixer(h, w: Dict[str, torch.Tensor], m: dict, eps: float):
     """Gated delta rule with a decay per key channel.  h [T, D]; w holds the mixer's tensors by their short names."""
     T = h.shape[0]
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, dk = m["heads"], m["dim"]
+    G, dv = m.get("kv_heads", H), m.get("vdim", dk)
     q = silu(causal_conv(h @ w["q"].T, w["q.conv"])).reshape(T, G, dk)
     k = silu(causal_conv(h @ w["k"].T, w["k.conv"])).reshape(T, G, dk)
     v = silu(causal_conv(h @ w["v"].T, w["v.conv"])).reshape(T, H, dv)
@@ -99,7 +100,8 @@ def talking_window_attention(h, positions, w, m: dict, eps: float):
     """Softmax attention over a sliding window with capped scores that are mixed across heads before the softmax,
     and a sink per head in the denominator."""
     T = h.shape[0]
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, dk = m["heads"], m["dim"]
+    G, dv = m.get("kv_heads", H), m.get("vdim", dk)
     q = (h @ w["q"].T + w["q.b"]).reshape(T, H, dk)
     k = (h @ w["k"].T + w["k.b"]).reshape(T, G, dk)
     v = (h @ w["v"].T + w["v.b"]).reshape(T, G, dv)
@@ -152,8 +154,8 @@ def sub(w: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
 
 
 def parallel_mixer(h, positions, w, m: dict, eps: float):
-    return (m["left_scale"] * talking_window_attention(h, positions, sub(w, "left."), m["left"], eps)
-            + m["right_scale"] * general_delta_mixer(h, sub(w, "right."), m["right"], eps))
+    return (m.get("left_scale", 1.0) * talking_window_attention(h, positions, sub(w, "left."), m["left"], eps)
+            + m.get("right_scale", 1.0) * general_delta_mixer(h, sub(w, "right."), m["right"], eps))
 
 
 # ------------------------------------------------------------------------------------------------ feed-forward
@@ -215,3 +217,79 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
         if layers_out is not None:
             layers_out.append(x.clone())
     return group_norm(x, w["final.norm"], groups, eps) @ w["head"].T
+
+
+# ------------------------------------------------------------------------------------------------ random models
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    """every tensor of a checkpoint of this configuration, by name.  The inner sizes of the two-matrix projections are
+    no configuration keys of a checkpoint (its tensor shapes give them); a test's dictionary carries them as
+    ``decay_rank`` / ``gate_rank`` beside the mixer's sizes."""
+    D, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, D), "embed.norm": (D,), "final.norm": (D,), "head": (V, D)}
+    if cfg.get("loop"):
+        s["loop.step"] = (cfg["loop"]["times"], D)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        s[p + "norm1"] = (D,)
+        if L["type"] == "channel_delta":
+            H, G, dk, dv, n = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"]), m.get("conv", 1)
+            x = p + "mix."
+            s.update({x + "q": (G * dk, D), x + "q.conv": (G * dk, n), x + "k": (G * dk, D), x + "k.conv": (G * dk, n),
+                      x + "v": (H * dv, D), x + "v.conv": (H * dv, n), x + "b": (H, D), x + "A_log": (H,), x + "norm": (dv,),
+                      x + "a1": (m["decay_rank"], D), x + "a2": (H * dk, m["decay_rank"]), x + "dt_bias": (H * dk,),
+                      x + "g1": (m["gate_rank"], D), x + "g2": (H * dv, m["gate_rank"]), x + "o": (D, H * dv)})
+        else:
+            a, r = m["left"], m["right"]
+            H, G, dk, dv = a["heads"], a.get("kv_heads", a["heads"]), a["dim"], a.get("vdim", a["dim"])
+            x, y, nr = p + "mix.left.", p + "mix.right.", r["heads"] * r["dim"]
+            s.update({x + "q": (H * dk, D), x + "q.b": (H * dk,), x + "k": (G * dk, D), x + "k.b": (G * dk,),
+                      x + "v": (G * dv, D), x + "v.b": (G * dv,), x + "q.norm": (dk,), x + "k.norm": (dk,),
+                      x + "talk": (H, H), x + "sink": (H,), x + "o": (D, H * dv)})
+            s.update({y + "r": (nr, D), y + "k": (nr, D), y + "v": (nr, D), y + "g": (nr, D), y + "a": (nr, D),
+                      y + "a.b": (nr,), y + "w1": (r["decay_rank"], D), y + "w2": (nr, r["decay_rank"]), y + "w0": (nr,),
+                      y + "norm": (nr,), y + "o": (D, nr)})
+        f = L.get("mlp")
+        if f:
+            s[p + "norm2"] = (D,)
+            x = p + "mlp."
+            if f["kind"] == "dense":
+                s.update({x + "up": (f["ff"], D), x + "down": (D, f["ff"])})
+            else:
+                E, F = f["router"]["experts"], f["expert"]["ff"]
+                s.update({x + "router": (E, D), x + "router.b": (E,)})
+                for e in range(E):
+                    s.update({x + f"e{e}.gate": (F, D), x + f"e{e}.up": (F, D), x + f"e{e}.down": (D, F)})
+                if f.get("shared"):
+                    Fs = f["shared"]["ff"]
+                    s.update({x + "shared.gate": (Fs, D), x + "shared.up": (Fs, D), x + "shared.down": (D, Fs)})
+    return s
+
+
+def random_model(cfg: dict, seed: int, scale: float = 1.0) -> Dict[str, torch.Tensor]:
+    """weights whose every mechanism matters in the logits: matrices of unit-variance outputs, norm weights around
+    one, a head mix that is far from the identity, sinks, biases and decay parameters of order one"""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        rnd = lambda: torch.randn(shape, generator=g)
+        if leaf in ("norm1", "norm2", "norm"):
+            t = 1.0 + 0.3 * rnd()
+        elif leaf == "conv":
+            t = 0.6 * rnd()
+        elif leaf == "talk":
+            t = torch.eye(shape[0]) + 0.4 * rnd()
+        elif leaf in ("sink", "A_log", "w0"):
+            t = rnd()
+        elif leaf == "dt_bias":
+            t = rnd() - 1.0
+        elif leaf == "b" and len(shape) == 1:
+            t = 0.5 * rnd()
+        elif leaf == "step":
+            t = 0.5 * rnd()
+        elif leaf == "embed":
+            t = rnd()
+        else:
+            t = rnd() * (scale / math.sqrt(shape[-1]))
+        w[name] = t.to(torch.bfloat16)          # what a checkpoint stores
+    return w
