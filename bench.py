@@ -671,10 +671,21 @@ def run_ours(args):
 
 
 def family_sizes(family="mezilix"):
-    """(label, configuration of the family, Qwen2 config of the same width, depth, head count and active weights per layer)"""
+    """(label, configuration of the family, configuration it is measured beside: for Mezilix and Rivetar a Qwen2 model of
+    the same width, depth, head count and active weights per layer; for Mavipel the Rivetar model of the same width,
+    depth and head count, whose recurrence and windowed attention are the like kernels)"""
     from asd_b200.models.qwen2 import Qwen2Config
     out = []
     for label, width, heads, layers in (("w2048", 2048, 16, 4), ("w4096", 4096, 32, 4)):
+        if family == "mavipel":
+            from asd_b200.models import mavipel, rivetar
+            layers = 6          # four gated-delta layers and two parallel ones (window attention + generalised delta rule)
+            fm = mavipel.sized_config(width, layers, heads, vocab=32768, dim=128, window=1024, ff=3 * width, experts=8, top=2,
+                                      name=f"mavipel-{label}")
+            rv = rivetar.sized_config(width, layers, heads, vocab=32768, dim=128, window=1024, keep_first=4, ff=3 * width,
+                                      name=f"rivetar-{label}")
+            out.append((label, fm, rv))
+            continue
         if family == "rivetar":
             from asd_b200.models import rivetar
             layers = 6          # two of every mixer: latent attention, gated linear attention, windowed attention
@@ -736,13 +747,53 @@ def rivetar_model(cfg, M, kv_len, nseq):
     return {k: tuple(v) for k, v in cls.items()}
 
 
+def mavipel_model(cfg, M, kv_len, nseq):
+    """algorithmic (FLOPs, bytes) of one forward per kernel class, summed over the layer executions (bf16 engine).
+    Recurrences: 7 (gated) or 9 (generalised) operations per state element and position as the rules are written;
+    bytes = the state in and out once per sequence plus a position's vectors."""
+    D = cfg.width
+    tri = 0.5 if M > nseq else 1.0
+    cls = {k: [0.0, 0.0] for k in ("dense", "window_attention", "recurrence", "experts")}
+
+    def add(k, fl, by):
+        cls[k][0] += fl
+        cls[k][1] += by
+    for i, _ in cfg.runs():
+        l = cfg.layers[i]
+        if l.type == "channel_delta":
+            nk, nv = l.kv_heads * l.dim, l.heads * l.vdim
+            n_in, mix = 2 * nk + nv + l.heads + l.decay_rank + l.gate_rank, nv
+            add("recurrence", 7.0 * M * l.heads * l.dim * l.vdim,
+                8.0 * nseq * l.heads * l.dim * l.vdim + 4.0 * M * (2 * nk + l.heads * l.dim + 2 * nv))
+        else:
+            kvw, nr = l.a_kv_heads * (l.a_dim + l.a_vdim), l.r_heads * l.r_dim
+            n_in, mix = l.a_heads * l.a_dim + kvw + 5 * nr + l.r_decay_rank, l.a_heads * l.a_vdim + nr
+            keys = min(l.window, kv_len)
+            add("window_attention", 2.0 * M * l.a_heads * keys * (l.a_dim + l.a_vdim + l.a_heads) * (tri if kv_len <= l.window else 1.0),
+                2.0 * nseq * (kv_len if M > nseq else keys) * kvw + 4.0 * M * l.a_heads * l.a_dim + 2.0 * M * l.a_heads * l.a_vdim)
+            add("recurrence", 9.0 * M * nr * l.r_dim, 8.0 * nseq * nr * l.r_dim + 4.0 * M * 6 * nr)
+        wd = (n_in + mix) * D
+        act = M * (2 * D + 4 * n_in + 2 * mix + 4 * D)
+        if l.ff_kind == "dense":
+            wd += 2 * l.ff * D
+            act += M * (2 * D + 6 * l.ff + 4 * D)
+        elif l.ff_kind == "moe":
+            hit = l.experts * (1.0 - (1.0 - l.top / l.experts) ** M)
+            add("experts", 2.0 * M * l.top * 3 * l.expert_ff * D,
+                2.0 * hit * 3 * l.expert_ff * D + M * l.top * (2.0 * D + 8.0 * l.expert_ff + 2.0 * l.expert_ff + 4.0 * D))
+            wd += 3 * l.shared_ff * D
+            act += M * (2 * D + 10 * l.shared_ff + 4 * D) if l.shared_ff else 0
+        add("dense", 2.0 * M * wd, 2.0 * wd + act)
+    return {k: tuple(v) for k, v in cls.items()}
+
+
 def family_model(cfg, M, kv_len, nseq, peaks):
     """algorithmic FLOPs and bytes of one forward of M tokens (nseq sequences, kv_len keys each) per kernel class"""
     import math
     L = cfg.num_hidden_layers
-    if getattr(cfg, "architecture", None) == "Rivetar":
-        L = 1           # rivetar_model already sums over the layer executions
-        cls = rivetar_model(cfg, M, kv_len, nseq)
+    if getattr(cfg, "architecture", None) in ("Rivetar", "Mavipel"):
+        L = 1           # these models already sum over the layer executions
+        cls = (rivetar_model if cfg.architecture == "Rivetar" else mavipel_model)(cfg, M, kv_len, nseq)
         head = (2.0 * nseq * cfg.vocab_size * cfg.width, 2.0 * cfg.vocab_size * cfg.width)
     elif getattr(cfg, "architecture", None) == "Mezilix":
         l, D = cfg.layers[0], cfg.width
@@ -773,14 +824,16 @@ def family_model(cfg, M, kv_len, nseq, peaks):
 
 
 def run_family(args):
-    """--family mezilix | rivetar: prefill and decode throughput of that family's engine at layer sizes of real models, beside the
-    Qwen2 engine at the same width, depth, head count and active weights per layer (random weights, synthetic tokens).
+    """--family mezilix | rivetar | mavipel: prefill and decode throughput of that family's engine at layer sizes of real
+    models, beside the Qwen2 engine at the same width, depth, head count and active weights per layer (Mavipel: beside
+    the Rivetar engine at the same width, depth and head count); random weights, synthetic tokens.
     Per kernel class: device time (CUDA events around every launch) against its floor = max(FLOPs / measured cuBLAS bf16
     rate, bytes / measured copy bandwidth).  Prints one JSON object; the default workload of this file is untouched."""
     import torch
     import asd_b200  # noqa: F401
-    from asd_b200.engine import MezilixEngine, QwenEngine, RivetarEngine
-    engines = {"mezilix": MezilixEngine, "rivetar": RivetarEngine, "qwen2": QwenEngine}
+    from asd_b200.engine import MavipelEngine, MezilixEngine, QwenEngine, RivetarEngine
+    from asd_b200.models import registry
+    engines = {"mezilix": MezilixEngine, "rivetar": RivetarEngine, "mavipel": MavipelEngine, "qwen2": QwenEngine}
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     peaks = json.load(open(path)) if os.path.exists(path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     dev = torch.device("cuda", 0)
@@ -794,7 +847,7 @@ def run_family(args):
     for label, mz_cfg, qw_cfg in family_sizes(args.family):
         if only & {"w2048", "w4096"} and label not in only:
             continue
-        for fam, cfg in ((args.family, mz_cfg), ("qwen2", qw_cfg)):
+        for fam, cfg in ((args.family, mz_cfg), (registry.family_of_config(qw_cfg).name, qw_cfg)):
             if only & set(engines) and fam not in only:
                 continue
             B = max(args.batch, 64)
@@ -880,7 +933,7 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="separate add+RMSNorm kernels instead of the fused epilogues")
     ap.add_argument("--nccl-only", action="store_true", help="TP boundaries through ncclAllReduce instead of the fused kernel")
     ap.add_argument("--opt", action="append", help="engine option name=value (e.g. pdl=0, attn_impl=0)")
-    ap.add_argument("--family", default=None, choices=["mezilix", "rivetar"],
+    ap.add_argument("--family", default=None, choices=["mezilix", "rivetar", "mavipel"],
                     help="instead of the default workload: prefill / decode throughput of this model family beside Qwen2 at equal size")
     args = ap.parse_args()
     if args.warmup < 3:
