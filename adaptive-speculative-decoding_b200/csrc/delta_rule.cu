@@ -182,15 +182,24 @@ __global__ void delta_prep_kernel(DeltaPrep p, int M) {
 }
 
 // ------------------------------------------------------------------------------------------ the recurrence
-constexpr int DR_CH = 16;   // positions staged per chunk
+__device__ __forceinline__ void cp_async4z(float* dst, const float* src, bool valid) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(dst);
+    const int sz = valid ? 4 : 0;       // 0: the destination is filled with zeros
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(addr), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(src) : "memory");
+}
 
 // ROWS state rows per thread; warps = slices of ROWS key rows (rows beyond dk are staged as zeros and keep a zero
-// state).  NV = 4: y is k (gated); NV = 5: y has its own vector (generalised).
+// state).  NV = 4: y is k (gated); NV = 5: y has its own vector (generalised).  CH positions are staged per chunk by
+// cp.async, one chunk ahead of the arithmetic.
 template <int ROWS, int NV, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
                                                                    const float* rv, const float* sc, const float* v,
                                                                    long long ldv, int heads, int dk, int dv, float* state,
-                                                                   int ring, float* out) {
+                                                                   int ring, float* out, int CH) {
     extern __shared__ __align__(16) float sm[];
     const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * 32;
     const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
@@ -201,11 +210,10 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
     const bool col_ok = col < dv;
     const int slot = seq_slot[seq];
     const int p0 = ix.positions[t0];
-    // shared: vecs [DR_CH][NV][dkp], v [DR_CH][32], scalars [DR_CH][4], partial sums [2][RS][2][32]
-    float* vec = sm;
-    float* vs = vec + DR_CH * NV * dkp;
-    float* ss = vs + DR_CH * 32;
-    float* red = ss + DR_CH * 4;
+    // shared: two buffers of { vectors [CH][NV][dkp], v [CH][32], scalars [CH][4] }, then the partial sums [2][RS][2][32]
+    const int buf_elems = CH * NV * dkp + CH * 36;
+    float* red = sm + 2 * buf_elems;
+    for (int i = threadIdx.x; i < 2 * buf_elems; i += nthr) sm[i] = 0.f;   // key rows beyond dk stay zero for good
     const long long st_head = ((long long)head * dk) * dv;
     const long long st_entry = (long long)heads * dk * dv;
     float* st_slot = state + (long long)slot * ring * st_entry;
@@ -219,21 +227,51 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
             if (r0 + r < dk) S[r] = src[(long long)(r0 + r) * dv + col];
     }
     const int hv = head * dv;
-    int par = 0;
-    for (int c0 = t0; c0 < t1; c0 += DR_CH) {
-        const int nt = min(DR_CH, t1 - c0);
-        __syncthreads();   // the previous chunk is consumed
-        for (int i = threadIdx.x; i < nt * NV * dkp; i += nthr) {
-            const int t = i / (NV * dkp), rest = i - t * NV * dkp;
-            const int j = rest / dkp, c = rest - j * dkp;
-            vec[i] = c < dk ? rv[(((long long)(c0 + t) * heads + head) * NV + j) * dk + c] : 0.f;
+    const bool v16 = (dk & 3) == 0;     // a (token, head)'s vectors then start on 16-byte boundaries
+    __syncthreads();
+    auto fetch = [&](int buf, int c0) {
+        const int nt = min(CH, t1 - c0);
+        float* vec = sm + buf * buf_elems;
+        float* vs = vec + CH * NV * dkp;
+        float* ss = vs + CH * 32;
+        if (v16) {
+            const int n4 = dk >> 2, per = NV * n4;
+            for (int i = threadIdx.x; i < nt * per; i += nthr) {
+                const int t = i / per, rest = i - t * per;
+                const int j = rest / n4, c4 = rest - j * n4;
+                cp_async16(vec + (t * NV + j) * dkp + 4 * c4, rv + (((long long)(c0 + t) * heads + head) * NV + j) * dk + 4 * c4);
+            }
+        } else {
+            const int per = NV * dk;
+            for (int i = threadIdx.x; i < nt * per; i += nthr) {
+                const int t = i / per, rest = i - t * per;
+                const int j = rest / dk, c = rest - j * dk;
+                cp_async4z(vec + (t * NV + j) * dkp + c, rv + (((long long)(c0 + t) * heads + head) * NV + j) * dk + c, true);
+            }
         }
         for (int i = threadIdx.x; i < nt * 32; i += nthr) {
             const int t = i >> 5, c = i & 31;
-            vs[i] = col0 + c < dv ? v[(long long)(c0 + t) * ldv + hv + col0 + c] : 0.f;
+            const bool ok = col0 + c < dv;
+            cp_async4z(vs + i, v + (ok ? (long long)(c0 + t) * ldv + hv + col0 + c : 0), ok);
         }
-        for (int i = threadIdx.x; i < nt * 4; i += nthr) ss[i] = sc[((long long)(c0 + (i >> 2)) * heads + head) * 4 + (i & 3)];
-        __syncthreads();
+        for (int i = threadIdx.x; i < nt * 4; i += nthr)
+            cp_async4z(ss + i, sc + ((long long)(c0 + (i >> 2)) * heads + head) * 4 + (i & 3), true);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, t0);
+    int par = 0, it = 0;
+    for (int c0 = t0; c0 < t1; c0 += CH, ++it) {
+        const int nt = min(CH, t1 - c0);
+        if (c0 + CH < t1) {
+            fetch((it + 1) & 1, c0 + CH);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();   // this chunk's rows have landed for every thread
+        const float* vec = sm + (it & 1) * buf_elems;
+        const float* vs = vec + CH * NV * dkp;
+        const float* ss = vs + CH * 32;
         for (int t = 0; t < nt; ++t, par ^= 1) {
             const float* vt = vec + t * NV * dkp + r0;
             const float4* d4 = reinterpret_cast<const float4*>(vt);
@@ -283,6 +321,7 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
                     if (r0 + r < dk) dst[(long long)(r0 + r) * dv + col] = S[r];
             }
         }
+        __syncthreads();   // the chunk is consumed: its buffer may be refilled
     }
 }
 
@@ -369,7 +408,10 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     while (rows < 32 && rows * 8 < dk) rows *= 2;
     const int RS = (dk + rows - 1) / rows;
     const int dkp = RS * rows, nv = general ? 5 : 4;
-    const size_t smem = (size_t)(DR_CH * nv * dkp + DR_CH * 32 + DR_CH * 4 + 2 * RS * 64) * sizeof(float);
+    int ch = 16;   // positions per staged chunk: as many as two buffers of a head's vectors leave room for
+    auto need = [&](int c) { return (size_t)(2 * (c * nv * dkp + c * 36) + 2 * RS * 64) * sizeof(float); };
+    while (ch > 1 && need(ch) > 200 * 1024) ch >>= 1;
+    const size_t smem = need(ch);
     if (smem > 220 * 1024) return set_error("delta rule: key size %d does not fit shared memory", dk);
     dim3 grid(nseq, heads, (dv + 31) / 32);
     if (grid.y > 65535 || grid.z > 65535) return set_error("delta rule: too many heads or value columns");
@@ -378,7 +420,7 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
         auto fn = delta_recurrence_kernel<R, NVV, T>;                                                                  \
         static PerDeviceOnce once;                                                                                    \
         if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
-        fn<<<grid, RS * 32, smem, stream>>>(ix, cu_q, seq_slot, rv, sc, v, ldv, heads, dk, dv, state, ring, out);      \
+        fn<<<grid, RS * 32, smem, stream>>>(ix, cu_q, seq_slot, rv, sc, v, ldv, heads, dk, dv, state, ring, out, ch);  \
     }
 #define ASD_DR_ROWS(NVV)                             \
     if (RS > 8) ASD_DR_CASE(32, NVV, 1024)           \

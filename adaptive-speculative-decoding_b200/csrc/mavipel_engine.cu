@@ -75,6 +75,7 @@ struct MvEngine : asd_mavipel_engine {
     std::vector<void*> owned;
     DenseRunner dn;
     EventProfiler prof;
+    AttnSplit attn_ws;           // partial sums of the window attention's key shares (steps of few tokens)
     int* dev_error = nullptr;
     int device = 0;
     const void* gw(const char* name) const {
@@ -178,7 +179,7 @@ static int mix_parallel(MvEngine* e, const MvLayer& ly, const MvRun& run, int li
     {
         MV_PROF(MV_ATTN);
         if (launch_talk_attention(b.ix, b.cu_q, b.seq_slot, b.nseq, b.max_qlen, b.max_kv_len, e->proj, ly.ld_in, td,
-                                  ly.f("talk"), ly.f("sink"), cache, e->mixed, f32, ly.mix_w, c.left_scale, s))
+                                  ly.f("talk"), ly.f("sink"), cache, e->mixed, f32, ly.mix_w, c.left_scale, e->attn_ws, s))
             return -1;
     }
     float* r = e->proj + nl;
@@ -395,7 +396,7 @@ asd_mavipel_engine_t* asd_mavipel_create(const asd_mavipel_config* cfg, const as
     e->esz = cfg->dtype ? 4 : 2;
     cudaGetDevice(&e->device);
     const size_t MT = cfg->max_tokens, D = cfg->width;
-    size_t ld_in = 4, conv = 1, nk = 1, nv = 1, rvn = 1, heads = 1, mixw = 1, upw = 1, actw = 1, E = 1, top = 1;
+    size_t ld_in = 4, conv = 1, nk = 1, nv = 1, rvn = 1, heads = 1, mixw = 1, upw = 1, actw = 1, E = 1, top = 1, share = 0;
     auto fail = [&](const char* what, int l) {
         set_error("asd_mavipel_create: %s (layer %d)", what, l);
         asd_mavipel_destroy(e);
@@ -430,6 +431,7 @@ asd_mavipel_engine_t* asd_mavipel_create(const asd_mavipel_config* cfg, const as
             ly.n_in = c.a_heads * c.a_dim + c.a_kv_heads * (c.a_dim + c.a_vdim) + 5 * nr + c.r_decay_rank;
             ly.mix_w = c.a_heads * c.a_vdim + nr;
             ly.cache_row = c.a_kv_heads * (c.a_dim + c.a_vdim);
+            share = std::max(share, (size_t)c.a_heads * (c.a_vdim + 2));
             ly.state_elems = (size_t)c.r_heads * c.r_dim * c.r_dim;
             nk = std::max(nk, (size_t)nr);
             nv = std::max(nv, (size_t)nr);
@@ -495,6 +497,9 @@ asd_mavipel_engine_t* asd_mavipel_create(const asd_mavipel_config* cfg, const as
     rc |= dev_alloc(e, &e->group_off, E + 1);
     rc |= dev_alloc(e, &e->sorted_tok, MT * top);
     rc |= dev_alloc(e, &e->slot_of, MT * top);
+    // key shares are used while CTAs are fewer than half the SMs: at most 148 x 8 (token, share) pairs
+    e->attn_ws.o_elems = (long long)(148 * 8 * share);
+    if (share) rc |= dev_alloc(e, &e->attn_ws.o, (size_t)e->attn_ws.o_elems);
     rc |= dev_alloc(e, &e->dev_error, 1);
     if (!rc && cudaMemset(e->dev_error, 0, sizeof(int)) != cudaSuccess) rc = -1;
     if (rc) {

@@ -5,10 +5,11 @@
 //   pairs (2 i, 2 i + 1), queries left in place, keys and values appended to the paged cache; one warp per (token, head).
 // talk_attention_kernel: one CTA per (sequence, TQ consecutive new positions), one warp per head.  Keys are visited in
 //   tiles of TK positions that start at multiples of TK (a position's sums run over the same tiles in the same order
-//   however its sequence was cut into forwards): the tile's keys and values are staged in shared memory as fp32 once
-//   for all heads and all TQ queries; lane = key for the scores (capped, stored for the other heads), then every warp
-//   mixes its head's row, folds it into the running softmax (which starts from the sink: maximum = sink, sum = 1,
-//   nothing accumulated) and adds the values with lane = value column.
+//   however its sequence was cut into forwards): the tile's cache rows are copied in 16-byte pieces, several in flight
+//   per lane, and staged in shared memory as fp32 once for all heads and all TQ queries; lane = key for the scores (a
+//   key coordinate is read once for the TQ queries; capped, stored for the other heads), then every warp mixes its
+//   head's row, folds it into the running softmax (which starts from the sink: maximum = sink, sum = 1, nothing
+//   accumulated) and adds the values with lane = value column (a value is read once for the TQ queries).
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -75,21 +76,64 @@ __global__ void talk_post_kernel(SeqIndex ix, float* qkv, long long ld, TalkDims
     }
 }
 
-// query positions per CTA at most: eight for up to 16 heads (512 threads, 128 registers each), two beyond
-
 struct TalkTile {
-    int tq, tk;            // query positions per CTA, key positions per tile (<= 32)
+    int tk;                // key positions per tile (<= 32)
     int ks_stride;         // floats per staged key row (odd: lanes = keys read without bank conflicts)
+    int vec;               // 1: cache rows are copied in 16-byte pieces
 };
 
-template <int DVL, int TA_TQ>
-__global__ void __launch_bounds__(TA_TQ > 2 ? 512 : 1024, 1) talk_attention_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
-                                                                 const float* q, long long ldq, TalkDims d, const float* talk,
-                                                                 const float* sink, PagedRows cache, void* out, int of32,
-                                                                 long long ldo, float out_scale, TalkTile tl) {
+// one cache row (keys, then values) -> fp32 in shared memory, 16 bytes per lane and load, four loads in flight
+template <typename T>
+__device__ __forceinline__ void stage_row_vec(const T* row, bool valid, float* kdst, float* vdst, int nk, int nv, int lane) {
+    constexpr int VE = 16 / sizeof(T);
+    const int nvec = (nk + nv) / VE;
+    for (int v0 = lane; v0 < nvec; v0 += 128) {
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + 32 * u;
+            r[u] = (valid && v < nvec) ? __ldg(reinterpret_cast<const uint4*>(row) + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + 32 * u;
+            if (v >= nvec) continue;
+            const int e = v * VE;
+            float* dst = e < nk ? kdst + e : vdst + (e - nk);
+            const T* x = reinterpret_cast<const T*>(&r[u]);
+#pragma unroll
+            for (int i = 0; i < VE; ++i) dst[i] = (float)x[i];
+        }
+    }
+}
+
+// TQ consecutive floats from shared memory (16-byte aligned for TQ >= 4, 8-byte for TQ = 2) in as few loads as possible
+template <int TQ>
+__device__ __forceinline__ void load_tq(const float* p, float (&r)[TQ]) {
+    if constexpr (TQ % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < TQ / 4; ++i) {
+            const float4 v = reinterpret_cast<const float4*>(p)[i];
+            r[4 * i] = v.x, r[4 * i + 1] = v.y, r[4 * i + 2] = v.z, r[4 * i + 3] = v.w;
+        }
+    } else if constexpr (TQ == 2) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        r[0] = v.x, r[1] = v.y;
+    } else {
+        r[0] = p[0];
+    }
+}
+
+// TQ query positions per CTA (compile time: a position's partial results live in registers), DVL = ceil(dv / 32)
+template <int DVL, int TQ>
+__global__ void __launch_bounds__(TQ > 2 ? 512 : 1024, 1) talk_attention_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
+                                                                         const float* q, long long ldq, TalkDims d,
+                                                                         const float* talk, const float* sink,
+                                                                         PagedRows cache, void* out, int of32, long long ldo,
+                                                                         float out_scale, TalkTile tl, float* part, int nsplit) {
     extern __shared__ __align__(16) float sm[];
     const int seq = blockIdx.y;
-    const int t0 = cu_q[seq] + blockIdx.x * tl.tq, t1 = min(cu_q[seq + 1], t0 + tl.tq);
+    const int t0 = cu_q[seq] + blockIdx.x * TQ, t1 = min(cu_q[seq + 1], t0 + TQ);
     if (t0 >= t1) return;
     const int nq = t1 - t0;
     const int H = d.heads, G = d.kv_heads, dk = d.dk, dv = d.dv, TK = tl.tk;
@@ -97,97 +141,165 @@ __global__ void __launch_bounds__(TA_TQ > 2 ? 512 : 1024, 1) talk_attention_kern
     const int kvh = h / (H / G);
     const int slot = seq_slot[seq];
     const int pos0 = ix.positions[t0], pos1 = pos0 + nq - 1;   // a sequence's new tokens are consecutive positions
-    float* qs = sm;                                   // [tq][H][dk]
-    float* Ks = qs + tl.tq * H * dk;                  // [TK][ks_stride]
-    float* Vs = Ks + TK * tl.ks_stride;               // [TK][G * dv]
-    float* Ss = Vs + TK * G * dv;                     // [tq][H][32]
-    float* Ts = Ss + tl.tq * H * 32;                  // [H][H]
-    for (int i = threadIdx.x; i < nq * H * dk; i += nthr) {
-        const int t = i / (H * dk), c = i - t * (H * dk);
-        qs[i] = q[(long long)(t0 + t) * ldq + c];
+    float* qs = sm;                                   // [H][dk][TQ]
+    float* Ks = qs + H * dk * TQ;                     // [TK][ks_stride]
+    float* Vs = Ks + ((TK * tl.ks_stride + 3) & ~3);  // [TK][G * dv]
+    float* Ss = Vs + ((TK * G * dv + 3) & ~3);        // [H][TQ][32] capped scores of every head
+    float* Ps = Ss + H * TQ * 32;                     // [H][32][TQ] softmax weights, private to the head's warp
+    float* Ts = Ps + H * 32 * TQ;                     // [H][H]
+    for (int i = threadIdx.x; i < H * dk * TQ; i += nthr) {
+        const int t = i % TQ, c = i / TQ;             // c = head * dk + coordinate
+        qs[i] = t < nq ? q[(long long)(t0 + t) * ldq + c] : 0.f;
     }
     for (int i = threadIdx.x; i < H * H; i += nthr) Ts[i] = talk ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
-    float mx[TA_TQ], sum[TA_TQ], O[TA_TQ][DVL];
+    float mx[TQ], sum[TQ], O[TQ][DVL];
+    const bool whole = nsplit <= 1;     // a share of the keys starts from nothing: the merge adds the sink once
 #pragma unroll
-    for (int t = 0; t < TA_TQ; ++t) {
-        mx[t] = sink ? sink[h] : -INFINITY;
-        sum[t] = sink ? 1.f : 0.f;
+    for (int t = 0; t < TQ; ++t) {
+        mx[t] = sink && whole ? sink[h] : -INFINITY;
+        sum[t] = sink && whole ? 1.f : 0.f;
 #pragma unroll
         for (int i = 0; i < DVL; ++i) O[t][i] = 0.f;
     }
     const int lo_pos = max(0, pos0 - d.window + 1);
-    const int row_elems = G * (dk + dv);
-    for (int kt = lo_pos / TK; kt <= pos1 / TK; ++kt) {
+    const int nk = G * dk, nv = G * dv, row_elems = nk + nv;
+    int kt_lo = lo_pos / TK, kt_hi = pos1 / TK;
+    if (!whole) {       // this CTA's share of the key tiles
+        const int per = (kt_hi - kt_lo + nsplit) / nsplit;
+        kt_lo += blockIdx.z * per;
+        kt_hi = min(kt_hi, kt_lo + per - 1);
+    }
+    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int j0 = kt * TK;
         __syncthreads();   // the previous tile is consumed (and, the first time, the queries are staged)
-        for (int i = threadIdx.x; i < TK * G * dk; i += nthr) {
-            const int t = i / (G * dk), c = i - t * (G * dk);
-            const int j = j0 + t;
-            Ks[t * tl.ks_stride + c] = j <= pos1 ? ldx(cache.pool, cache_row(cache, slot, j) * row_elems + c, cache.f32) : 0.f;
-        }
-        for (int i = threadIdx.x; i < TK * G * dv; i += nthr) {
-            const int t = i / (G * dv), c = i - t * (G * dv);
-            const int j = j0 + t;
-            Vs[i] = j <= pos1 ? ldx(cache.pool, cache_row(cache, slot, j) * row_elems + (long long)G * dk + c, cache.f32) : 0.f;
-        }
-        __syncthreads();
-        // scores of this warp's head: lane = key
-#pragma unroll
-        for (int t = 0; t < TA_TQ; ++t) {
-            if (t >= nq) break;
-            const int pi = pos0 + t;
-            if (j0 > pi || j0 + TK - 1 < pi - d.window + 1) continue;   // no key of the tile is visible
-            float s = 0.f;
-            if (lane < TK) {
-                const float* qv = qs + (t * H + h) * dk;
-                const float* kv = Ks + lane * tl.ks_stride + kvh * dk;
-                float s0 = 0.f, s1 = 0.f;
-                int c = 0;
-                for (; c + 1 < dk; c += 2) {
-                    s0 = fmaf(qv[c], kv[c], s0);
-                    s1 = fmaf(qv[c + 1], kv[c + 1], s1);
-                }
-                if (c < dk) s0 = fmaf(qv[c], kv[c], s0);
-                s = (s0 + s1) * d.scale;
-                if (d.softcap > 0.f) s = d.softcap * tanhf(s / d.softcap);
+        if (tl.vec) {
+            for (int t = h; t < TK; t += H) {
+                const int j = j0 + t;
+                const bool valid = j <= pos1;
+                const long long row = valid ? cache_row(cache, slot, j) * row_elems : 0;
+                if (cache.f32)
+                    stage_row_vec(static_cast<const float*>(cache.pool) + row, valid, Ks + t * tl.ks_stride, Vs + t * nv, nk, nv, lane);
+                else
+                    stage_row_vec(static_cast<const __nv_bfloat16*>(cache.pool) + row, valid, Ks + t * tl.ks_stride, Vs + t * nv,
+                                  nk, nv, lane);
             }
-            Ss[(t * H + h) * 32 + lane] = s;
+        } else {
+            for (int i = threadIdx.x; i < TK * row_elems; i += nthr) {
+                const int t = i / row_elems, c = i - t * row_elems;
+                const int j = j0 + t;
+                const float v = j <= pos1 ? ldx(cache.pool, cache_row(cache, slot, j) * row_elems + c, cache.f32) : 0.f;
+                if (c < nk)
+                    Ks[t * tl.ks_stride + c] = v;
+                else
+                    Vs[t * nv + c - nk] = v;
+            }
+        }
+        __syncthreads();
+        {   // scores of this warp's head for all TQ positions: lane = key, a key coordinate is read once for all of them
+            float s[TQ];
+#pragma unroll
+            for (int t = 0; t < TQ; ++t) s[t] = 0.f;
+            if (lane < TK) {
+                const float* qh = qs + (long long)h * dk * TQ;
+                const float* kp = Ks + lane * tl.ks_stride + kvh * dk;
+#pragma unroll 4
+                for (int c = 0; c < dk; ++c) {
+                    const float kc = kp[c];
+                    float qc[TQ];
+                    load_tq<TQ>(qh + c * TQ, qc);
+#pragma unroll
+                    for (int t = 0; t < TQ; ++t) s[t] = fmaf(qc[t], kc, s[t]);
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < TQ; ++t) {
+                float v = s[t] * d.scale;
+                if (d.softcap > 0.f) v = d.softcap * tanhf(v / d.softcap);
+                Ss[(h * TQ + t) * 32 + lane] = v;
+            }
         }
         __syncthreads();
 #pragma unroll
-        for (int t = 0; t < TA_TQ; ++t) {
-            if (t >= nq) break;
+        for (int t = 0; t < TQ; ++t) {
             const int pi = pos0 + t;
-            if (j0 > pi || j0 + TK - 1 < pi - d.window + 1) continue;
             float s = 0.f;
-            for (int g = 0; g < H; ++g) s = fmaf(Ts[h * H + g], Ss[(t * H + g) * 32 + lane], s);
+            for (int g = 0; g < H; ++g) s = fmaf(Ts[h * H + g], Ss[(g * TQ + t) * 32 + lane], s);
             const int j = j0 + lane;
-            const bool ok = lane < TK && j <= pi && pi - j < d.window;
-            const float tile_max = warp_max(ok ? s : -INFINITY);
-            const float m_new = fmaxf(mx[t], tile_max);
+            const bool ok = t < nq && lane < TK && j <= pi && pi - j < d.window;
+            const float m_new = fmaxf(mx[t], warp_max(ok ? s : -INFINITY));
             const float p = ok ? expf(s - m_new) : 0.f;
-            const float corr = mx[t] == -INFINITY ? 0.f : expf(mx[t] - m_new);
+            const float corr = mx[t] == -INFINITY ? 0.f : expf(mx[t] - m_new);   // a position that has seen nothing yet keeps zeros
             sum[t] = sum[t] * corr + warp_sum(p);
             mx[t] = m_new;
 #pragma unroll
             for (int i = 0; i < DVL; ++i) O[t][i] *= corr;
+            Ps[(h * 32 + lane) * TQ + t] = p;
+        }
+        __syncwarp();
+        {   // values: lane = value column, a value is read once for all TQ positions
             const float* vb = Vs + kvh * dv + lane;
+            const float* pb = Ps + (long long)h * 32 * TQ;
             for (int k = 0; k < TK; ++k) {
-                const float pk = __shfl_sync(0xffffffffu, p, k);
-                if (pk == 0.f) continue;       // uniform over the warp
+                float pk[TQ];
+                load_tq<TQ>(pb + k * TQ, pk);
 #pragma unroll
-                for (int i = 0; i < DVL; ++i)
-                    if (lane + 32 * i < dv) O[t][i] = fmaf(pk, vb[k * G * dv + 32 * i], O[t][i]);
+                for (int i = 0; i < DVL; ++i) {
+                    if (lane + 32 * i < dv) {
+                        const float vv = vb[k * nv + 32 * i];
+#pragma unroll
+                        for (int t = 0; t < TQ; ++t) O[t][i] = fmaf(pk[t], vv, O[t][i]);
+                    }
+                }
             }
         }
+        __syncwarp();
+    }
+    if (!whole) {       // unnormalised sums, maximum and denominator of this share: [row][share][head][dv + 2]
+#pragma unroll
+        for (int t = 0; t < TQ; ++t) {
+            if (t >= nq) continue;
+            float* dst = part + (((long long)(t0 + t) * nsplit + blockIdx.z) * H + h) * (dv + 2);
+#pragma unroll
+            for (int i = 0; i < DVL; ++i)
+                if (lane + 32 * i < dv) dst[lane + 32 * i] = O[t][i];
+            if (lane == 0) dst[dv] = mx[t], dst[dv + 1] = sum[t];
+        }
+        return;
     }
 #pragma unroll
-    for (int t = 0; t < TA_TQ; ++t) {
-        if (t >= nq) break;
+    for (int t = 0; t < TQ; ++t) {
+        if (t >= nq) continue;
         const float r = out_scale / sum[t];
 #pragma unroll
         for (int i = 0; i < DVL; ++i)
             if (lane + 32 * i < dv) stx(out, (long long)(t0 + t) * ldo + (long long)h * dv + lane + 32 * i, of32, O[t][i] * r);
+    }
+}
+
+// one warp per (token, head): the shares' sums brought to a common maximum, the sink entering once
+__global__ void talk_merge_kernel(const float* part, int nsplit, const float* sink, void* out, int of32, long long ldo,
+                                  float out_scale, int M, int H, int dv) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (idx >= (long long)M * H) return;
+    const int m = (int)(idx / H), h = (int)(idx - (long long)m * H);
+    const float* base = part + ((long long)m * nsplit * H + h) * (dv + 2);
+    const long long step = (long long)H * (dv + 2);
+    float top = sink ? sink[h] : -INFINITY;
+    for (int s = 0; s < nsplit; ++s) top = fmaxf(top, base[s * step + dv]);
+    float den = sink ? expf(sink[h] - top) : 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = base[s * step + dv];
+        if (ms != -INFINITY) den += base[s * step + dv + 1] * expf(ms - top);
+    }
+    const float r = out_scale / den;
+    for (int c = lane; c < dv; c += 32) {
+        float o = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float ms = base[s * step + dv];
+            if (ms != -INFINITY) o = fmaf(base[s * step + c], expf(ms - top), o);
+        }
+        stx(out, (long long)m * ldo + (long long)h * dv + c, of32, o * r);
     }
 }
 
@@ -206,31 +318,43 @@ int launch_talk_post(const SeqIndex& ix, float* qkv, long long ld, const TalkDim
 
 int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
                           const float* q, long long ldq, const TalkDims& d, const float* talk, const float* sink,
-                          const PagedRows& cache, void* out, int of32, long long ldo, float out_scale, cudaStream_t stream) {
+                          const PagedRows& cache, void* out, int of32, long long ldo, float out_scale, const AttnSplit& ws,
+                          cudaStream_t stream) {
     if (ix.M <= 0 || nseq <= 0) return 0;
-    (void)max_kv_len;
     if (d.heads <= 0 || d.heads > 32 || d.kv_heads <= 0 || d.heads % d.kv_heads)
         return set_error("talk_attention: %d heads (at most 32) over %d key/value heads", d.heads, d.kv_heads);
     if (d.dv > 256 || d.dv <= 0 || d.dk <= 0 || d.window <= 0) return set_error("talk_attention: bad sizes");
-    // the largest tile that fits shared memory; it depends on the layer's sizes alone, never on the batch
-    static const int kTiles[][2] = {{8, 32}, {4, 32}, {8, 16}, {2, 32}, {4, 16}, {1, 32}, {2, 16}, {1, 16}, {1, 8}, {1, 4}, {1, 2}, {1, 1}};
-    TalkTile tl{0, 0, 0};
-    size_t smem = 0;
-    const int tq_max = d.heads > 16 ? 2 : 8;
-    for (const auto& c : kTiles) {
-        if (c[0] > tq_max) continue;
-        const int ks = (d.kv_heads * d.dk) | 1;
-        const size_t need = ((size_t)c[0] * d.heads * d.dk + (size_t)c[1] * ks + (size_t)c[1] * d.kv_heads * d.dv +
-                             (size_t)c[0] * d.heads * 32 + (size_t)d.heads * d.heads) * sizeof(float);
-        if (need <= 200 * 1024) {
-            tl = TalkTile{c[0], c[1], ks};
-            smem = need;
-            break;
-        }
-    }
-    if (!tl.tq) return set_error("talk_attention: the heads' rows do not fit shared memory");
-    dim3 grid((max_qlen + tl.tq - 1) / tl.tq, nseq);
+    // Key tile and query tile from the layer's sizes (the key tile never depends on the batch: a position's sums run over
+    // the same tiles whatever it is fed with); single-token steps take one query position per CTA.
+    const int esz = cache.f32 ? 4 : 2, ve = 16 / esz;
+    const int ks = (d.kv_heads * d.dk) | 1;
+    auto need = [&](int tq, int tk) {
+        return ((size_t)tq * d.heads * d.dk + (((size_t)tk * ks + 3) & ~(size_t)3) + (((size_t)tk * d.kv_heads * d.dv + 3) & ~(size_t)3) +
+                2 * (size_t)tq * d.heads * 32 + (size_t)d.heads * d.heads) * sizeof(float);
+    };
+    int tk = 32;
+    while (tk > 1 && need(1, tk) > 200 * 1024) tk >>= 1;
+    if (need(1, tk) > 200 * 1024) return set_error("talk_attention: the heads' rows do not fit shared memory");
+    int tq = d.heads > 16 ? 2 : 8;
+    while (tq > 1 && (need(tq, tk) > 200 * 1024 || tq >= 2 * max_qlen)) tq >>= 1;
+    TalkTile tl{tk, ks, 0};
+    tl.vec = (d.kv_heads * d.dk) % ve == 0 && (d.kv_heads * d.dv) % ve == 0 && (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0;
+    const size_t smem = need(tq, tk);
+    dim3 grid((max_qlen + tq - 1) / tq, nseq);
     if (grid.y > 65535) return set_error("talk_attention: too many sequences");
+    // few CTAs and many key tiles (single-token steps of a few sequences): the key tiles are cut into shares for several
+    // CTAs, whose partial sums a second kernel merges
+    int nsplit = 1;
+    const long long ctas = (long long)grid.x * grid.y;
+    const int tiles = (int)((long long)(d.window < max_kv_len ? d.window : max_kv_len) + tq) / tk + 1;
+    if (ws.o && ctas * 2 <= 148 && tiles >= 4) {
+        nsplit = (int)(148 / ctas);
+        if (nsplit > tiles / 2) nsplit = tiles / 2;
+        const long long per_share = (long long)ix.M * d.heads * (d.dv + 2);
+        if ((long long)nsplit * per_share > ws.o_elems) nsplit = (int)(ws.o_elems / per_share);
+        if (nsplit < 2) nsplit = 1;
+    }
+    grid.z = nsplit;
     const int dvl = (d.dv + 31) / 32;
 #define ASD_TA_CASE2(L, Q)                                                                                            \
     {                                                                                                                 \
@@ -238,11 +362,13 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
         static PerDeviceOnce once;                                                                                    \
         if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
         fn<<<grid, d.heads * 32, smem, stream>>>(ix, cu_q, seq_slot, q, ldq, d, talk, sink, cache, out, of32, ldo,     \
-                                                 out_scale, tl);                                                      \
+                                                 out_scale, tl, ws.o, nsplit);                                        \
     }
-#define ASD_TA_CASE(L)                     \
-    if (tq_max == 8) ASD_TA_CASE2(L, 8)    \
-    else ASD_TA_CASE2(L, 2)
+#define ASD_TA_CASE(L)                      \
+    if (tq == 8) ASD_TA_CASE2(L, 8)         \
+    else if (tq == 4) ASD_TA_CASE2(L, 4)    \
+    else if (tq == 2) ASD_TA_CASE2(L, 2)    \
+    else ASD_TA_CASE2(L, 1)
     if (dvl <= 1) {
         ASD_TA_CASE(1)
     } else if (dvl <= 2) {
@@ -254,6 +380,12 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
     }
 #undef ASD_TA_CASE
 #undef ASD_TA_CASE2
+    if (nsplit > 1) {
+        const long long warps = (long long)ix.M * d.heads;
+        talk_merge_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(ws.o, nsplit, sink, out, of32, ldo, out_scale, ix.M,
+                                                                         d.heads, d.dv);
+        count_launch(1);
+    }
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;

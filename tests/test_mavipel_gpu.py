@@ -447,6 +447,30 @@ def test_far_key_among_hundreds_without_a_mask_and_first_tokens():
         close(eng)
 
 
+def test_single_token_steps_with_key_shares_over_several_ctas():
+    """a long window and few sequences: single-token steps (and portions of two) cut the key tiles into shares for
+    several CTAs and merge them, with the sink entering once, after the merge; two sequences of unequal length"""
+    cfg = config([par(heads=4, kv_heads=2, dim=32, vdim=40, size=800, rot_dims=16, scale=0.3)])
+    w = O.random_model(cfg, seed=47)
+    w["l0.mix.left.sink"] = torch.tensor([4.0, -1.0, 0.0, 2.0]).to(torch.bfloat16)
+    a, b = tokens(900, 120, 48), tokens(300, 120, 49)
+    ra, rb = oracle(cfg, w, a), oracle(cfg, w, b)
+    for dtype in (torch.float32, torch.bfloat16):
+        eng = make_engine(cfg, w, dtype=dtype, max_tokens=1024, max_seq_len=1024)
+        sa, sb = eng.open_sequence(), eng.open_sequence()
+        eng.reserve(sa, 900), eng.reserve(sb, 300)
+        eng.forward_ragged([(sa, 0, a[:870], []), (sb, 0, b[:270], [])])
+        ga, gb = [], []
+        for i in range(15):
+            n = 2
+            out = eng.forward_ragged([(sa, 870 + n * i, a[870 + n * i:870 + n * (i + 1)], list(range(n))),
+                                      (sb, 270 + n * i, b[270 + n * i:270 + n * (i + 1)], list(range(n)))])
+            ga.append(out[:n]), gb.append(out[n:])
+        for got, ref in ((torch.cat(ga), ra[870:]), (torch.cat(gb), rb[270:])):
+            assert (rel_err(got, ref)[1] < 2e-4) if dtype == torch.float32 else (rel_err(got, ref)[0] < 5e-2)
+        close(eng)
+
+
 def random_config(seed):
     """layers in any order and number with sizes drawn at random (multiples of 16 and of nothing), a span anywhere"""
     g = torch.Generator().manual_seed(seed)
