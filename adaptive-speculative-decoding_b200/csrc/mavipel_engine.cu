@@ -585,6 +585,10 @@ int asd_mavipel_set_option(asd_mavipel_engine_t* h, const char* name, int value)
         e->dn.clear();
         return 0;
     }
+    if (!strcmp(name, "attn_mma")) {
+        e->attn_ws.tiled = value;
+        return 0;
+    }
     if (!strcmp(name, "profile")) {
         e->prof.on = value;
         e->prof.reset();

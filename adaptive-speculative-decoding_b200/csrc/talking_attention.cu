@@ -16,6 +16,7 @@
 #include "asd_internal.h"
 #include "blocks.h"
 #include "elem.cuh"
+#include "mma_sync.cuh"
 
 namespace asd {
 
@@ -149,7 +150,11 @@ __global__ void __launch_bounds__(TQ > 2 ? 512 : 1024, 1) talk_attention_kernel(
     float* Ts = Ps + H * 32 * TQ;                     // [H][H]
     for (int i = threadIdx.x; i < H * dk * TQ; i += nthr) {
         const int t = i % TQ, c = i / TQ;             // c = head * dk + coordinate
-        qs[i] = t < nq ? q[(long long)(t0 + t) * ldq + c] : 0.f;
+        float qv = t < nq ? q[(long long)(t0 + t) * ldq + c] : 0.f;
+        // bf16 cache rows: the queries take the keys' precision, as in the tensor-core form, so that a position's
+        // scores are the same products whichever kernel serves its step
+        if (!cache.f32) qv = __bfloat162float(__float2bfloat16(qv));
+        qs[i] = qv;
     }
     for (int i = threadIdx.x; i < H * H; i += nthr) Ts[i] = talk ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
     float mx[TQ], sum[TQ], O[TQ][DVL];
@@ -276,6 +281,209 @@ __global__ void __launch_bounds__(TQ > 2 ? 512 : 1024, 1) talk_attention_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------------------------- tensor-core form
+// bf16 cache rows, 16 query positions per CTA, one warp per head, key tiles of 32 positions (multiples of 32, as above).
+// Queries are rounded to bf16 once; keys and values arrive by cp.async in the cache's bf16 and are read through
+// ldmatrix.  Per tile: S = Q K^T on mma.sync m16n8k16 (fp32 accumulation), scale and cap in registers, every head's
+// scores to shared memory, barrier; the key buffer is free and the next tile's keys start to arrive while each warp
+// mixes its head's scores (fp32, in the accumulator's own layout), updates the running softmax and multiplies the
+// weights, as two bf16 terms (value + residual), with the values; barrier; the next tile's values start to arrive.
+constexpr int TM_TK = 32, TM_TQ = 16, TM_SS = 40;   // key tile, query tile, floats per score row (32 + padding)
+
+template <int NDV>   // value size / 8
+__global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
+                                                                    const float* q, long long ldq, TalkDims d,
+                                                                    const float* talk, const float* sink, PagedRows cache,
+                                                                    void* out, int of32, long long ldo, float out_scale) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int seq = blockIdx.y;
+    const int t0 = cu_q[seq] + blockIdx.x * TM_TQ, t1 = min(cu_q[seq + 1], t0 + TM_TQ);
+    if (t0 >= t1) return;
+    const int nq = t1 - t0;
+    const int H = d.heads, G = d.kv_heads, dk = d.dk;
+    constexpr int dv = NDV * 8;
+    const int lane = threadIdx.x & 31, h = threadIdx.x >> 5, nthr = blockDim.x;
+    const int kvh = h / (H / G);
+    const int slot = seq_slot[seq];
+    const int pos0 = ix.positions[t0], pos1 = pos0 + nq - 1;
+    const int qstride = H * dk + 8, kstride = G * dk + 8, vstride = G * dv + 8;     // bf16 elements; rows 16 bytes apart mod 128
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [16][qstride]
+    __nv_bfloat16* Ks = Qs + TM_TQ * qstride;                                     // [32][kstride]
+    __nv_bfloat16* Vs = Ks + TM_TK * kstride;                                     // [32][vstride]
+    float* Ss = reinterpret_cast<float*>(Vs + TM_TK * vstride);                   // [H][16][TM_SS]
+    float* Ts = Ss + H * TM_TQ * TM_SS;                                           // [H][H]
+    for (int i = threadIdx.x; i < TM_TQ * H * dk; i += nthr) {
+        const int t = i / (H * dk), c = i - t * (H * dk);
+        Qs[t * qstride + c] = __float2bfloat16(t < nq ? q[(long long)(t0 + t) * ldq + c] : 0.f);
+    }
+    for (int i = threadIdx.x; i < H * H; i += nthr) Ts[i] = talk ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+    const int nk = G * dk, nv = G * dv, row_elems = nk + nv;
+    const __nv_bfloat16* pool = static_cast<const __nv_bfloat16*>(cache.pool);
+    const int kvec = nk / 8, vvec = nv / 8;
+    auto fetch_k = [&](int kt) {
+        if (kt >= 0) {
+            for (int i = threadIdx.x; i < TM_TK * kvec; i += nthr) {
+                const int t = i / kvec, c = i - t * kvec;
+                const int j = kt * TM_TK + t;
+                const bool ok = j <= pos1;
+                const __nv_bfloat16* src = pool + (ok ? cache_row(cache, slot, j) * row_elems + c * 8 : 0);
+                cp_async16((uint32_t)__cvta_generic_to_shared(Ks + t * kstride + c * 8), src, ok);
+            }
+        }
+        cp_async_commit();
+    };
+    auto fetch_v = [&](int kt) {
+        if (kt >= 0) {
+            for (int i = threadIdx.x; i < TM_TK * vvec; i += nthr) {
+                const int t = i / vvec, c = i - t * vvec;
+                const int j = kt * TM_TK + t;
+                const bool ok = j <= pos1;
+                const __nv_bfloat16* src = pool + (ok ? cache_row(cache, slot, j) * row_elems + nk + c * 8 : 0);
+                cp_async16((uint32_t)__cvta_generic_to_shared(Vs + t * vstride + c * 8), src, ok);
+            }
+        }
+        cp_async_commit();
+    };
+    const int gq = lane >> 2, tq = lane & 3;          // accumulator rows gq and gq + 8, columns 8 n + 2 tq + {0, 1}
+    float O[NDV][4];
+#pragma unroll
+    for (int n = 0; n < NDV; ++n) O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.f;
+    const float m0 = sink ? sink[h] : -INFINITY;
+    float mrow[2] = {m0, m0}, lrow[2] = {0.f, 0.f};
+    const int kt_lo = max(0, pos0 - d.window + 1) / TM_TK, kt_hi = pos1 / TM_TK;
+    fetch_k(kt_lo);
+    fetch_v(kt_lo);
+    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (lane & 15) * qstride + h * dk + (lane >> 4) * 8);
+    const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + ((lane & 7) + (lane >> 4) * 8) * kstride + kvh * dk + ((lane >> 3) & 1) * 8);
+    const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * vstride + kvh * dv + (lane >> 4) * 8);
+    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+        const int j0 = kt * TM_TK;
+        cp_async_wait<1>();      // this tile's keys (its values may still be on their way)
+        __syncthreads();
+        float acc[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        for (int ks = 0; ks < dk; ks += 16) {
+            uint32_t a[4], b[4];
+            ldsm_x4(q_addr + ks * 2, a);
+#pragma unroll
+            for (int n2 = 0; n2 < 2; ++n2) {
+                ldsm_x4(k_addr + (n2 * 16 * kstride + ks) * 2, b);
+                mma_bf16(acc[2 * n2], a, b[0], b[1]);
+                mma_bf16(acc[2 * n2 + 1], a, b[2], b[3]);
+            }
+        }
+        float* sh = Ss + (h * TM_TQ) * TM_SS;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = acc[n][i] * d.scale;
+                if (d.softcap > 0.f) v = d.softcap * tanhf(v / d.softcap);
+                acc[n][i] = v;
+            }
+            *reinterpret_cast<float2*>(sh + gq * TM_SS + 8 * n + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
+            *reinterpret_cast<float2*>(sh + (gq + 8) * TM_SS + 8 * n + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+        }
+        __syncthreads();         // every head's scores are there; the key buffer is free
+        fetch_k(kt < kt_hi ? kt + 1 : -1);
+#pragma unroll
+        for (int n = 0; n < 4; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+        for (int g = 0; g < H; ++g) {
+            const float w = Ts[h * H + g];
+            const float* sg = Ss + (g * TM_TQ) * TM_SS + 2 * tq;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const float2 lo = *reinterpret_cast<const float2*>(sg + gq * TM_SS + 8 * n);
+                const float2 hi = *reinterpret_cast<const float2*>(sg + (gq + 8) * TM_SS + 8 * n);
+                acc[n][0] = fmaf(w, lo.x, acc[n][0]);
+                acc[n][1] = fmaf(w, lo.y, acc[n][1]);
+                acc[n][2] = fmaf(w, hi.x, acc[n][2]);
+                acc[n][3] = fmaf(w, hi.y, acc[n][3]);
+            }
+        }
+        // mask, running maximum and weights of rows gq (r = 0) and gq + 8 (r = 1)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = gq + 8 * r, pi = pos0 + row;
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int j = j0 + 8 * n + 2 * tq + c;
+                    const bool ok = row < nq && j <= pi && pi - j < d.window;
+                    if (!ok) acc[n][2 * r + c] = -INFINITY;
+                    tmax = fmaxf(tmax, acc[n][2 * r + c]);
+                }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float m_new = fmaxf(mrow[r], tmax);
+            const float corr = mrow[r] == -INFINITY ? 0.f : expf(mrow[r] - m_new);
+            float part = 0.f;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const float sv = acc[n][2 * r + c];
+                    const float p = sv == -INFINITY ? 0.f : expf(sv - m_new);
+                    acc[n][2 * r + c] = p;
+                    part += p;
+                }
+            lrow[r] = lrow[r] * corr + part;
+            mrow[r] = m_new;
+#pragma unroll
+            for (int n = 0; n < NDV; ++n) {
+                O[n][2 * r] *= corr;
+                O[n][2 * r + 1] *= corr;
+            }
+        }
+        cp_async_wait<1>();      // this tile's values
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {        // 16 keys per step
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float x0 = acc[2 * j + (i >> 1)][2 * (i & 1)], x1 = acc[2 * j + (i >> 1)][2 * (i & 1) + 1];
+                const __nv_bfloat16 h0 = __float2bfloat16(x0), h1 = __float2bfloat16(x1);
+                __nv_bfloat162 hv;
+                hv.x = h0, hv.y = h1;
+                ph[i] = *reinterpret_cast<uint32_t*>(&hv);
+                pl[i] = pack_bf16(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+            }
+#pragma unroll
+            for (int n = 0; n < NDV; n += 2) {
+                uint32_t b[4];
+                ldsm_x4_t(v_addr + (j * 16 * vstride + n * 8) * 2, b);
+                mma_bf16(O[n], ph, b[0], b[1]);
+                mma_bf16(O[n], pl, b[0], b[1]);
+                mma_bf16(O[n + 1], ph, b[2], b[3]);
+                mma_bf16(O[n + 1], pl, b[2], b[3]);
+            }
+        }
+        __syncthreads();         // the value buffer is free
+        fetch_v(kt < kt_hi ? kt + 1 : -1);
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = gq + 8 * r;
+        float l = lrow[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (sink) l += expf(sink[h] - mrow[r]);
+        if (row >= nq) continue;
+        const float sc = out_scale / l;
+#pragma unroll
+        for (int n = 0; n < NDV; ++n) {
+            const long long o = (long long)(t0 + row) * ldo + (long long)h * dv + 8 * n + 2 * tq;
+            stx(out, o, of32, O[n][2 * r] * sc);
+            stx(out, o + 1, of32, O[n][2 * r + 1] * sc);
+        }
+    }
+}
+
 // one warp per (token, head): the shares' sums brought to a common maximum, the sink entering once
 __global__ void talk_merge_kernel(const float* part, int nsplit, const float* sink, void* out, int of32, long long ldo,
                                   float out_scale, int M, int H, int dv) {
@@ -324,6 +532,33 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
     if (d.heads <= 0 || d.heads > 32 || d.kv_heads <= 0 || d.heads % d.kv_heads)
         return set_error("talk_attention: %d heads (at most 32) over %d key/value heads", d.heads, d.kv_heads);
     if (d.dv > 256 || d.dv <= 0 || d.dk <= 0 || d.window <= 0) return set_error("talk_attention: bad sizes");
+    // bf16 cache rows and sizes that fill the tensor-core fragments: prompts and portions take the mma.sync kernel
+    if (ws.tiled && !cache.f32 && max_qlen >= 8 && d.heads <= 16 && d.dk % 16 == 0 &&
+        (d.dv == 16 || d.dv == 32 || d.dv == 64 || d.dv == 128) && (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0) {
+        const size_t smem = (size_t)(TM_TQ * (d.heads * d.dk + 8) + TM_TK * (d.kv_heads * d.dk + 8) +
+                                     TM_TK * (d.kv_heads * d.dv + 8)) * 2 +
+                            (size_t)(d.heads * TM_TQ * TM_SS + d.heads * d.heads) * sizeof(float);
+        if (smem <= 220 * 1024) {
+            dim3 grid((max_qlen + TM_TQ - 1) / TM_TQ, nseq);
+            if (grid.y > 65535) return set_error("talk_attention: too many sequences");
+#define ASD_TM_CASE(N)                                                                                                \
+    {                                                                                                                 \
+        auto fn = talk_attention_mma_kernel<N>;                                                                       \
+        static PerDeviceOnce once;                                                                                    \
+        if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+        fn<<<grid, d.heads * 32, smem, stream>>>(ix, cu_q, seq_slot, q, ldq, d, talk, sink, cache, out, of32, ldo,     \
+                                                 out_scale);                                                          \
+    }
+            if (d.dv == 16) ASD_TM_CASE(2)
+            else if (d.dv == 32) ASD_TM_CASE(4)
+            else if (d.dv == 64) ASD_TM_CASE(8)
+            else ASD_TM_CASE(16)
+#undef ASD_TM_CASE
+            count_launch(1);
+            ASD_CUDA(cudaGetLastError());
+            return 0;
+        }
+    }
     // Key tile and query tile from the layer's sizes (the key tile never depends on the batch: a position's sums run over
     // the same tiles whatever it is fed with); single-token steps take one query position per CTA.
     const int esz = cache.f32 ? 4 : 2, ve = 16 / esz;

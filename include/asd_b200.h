@@ -458,7 +458,8 @@ ASD_API size_t asd_mavipel_cache_bytes(const asd_mavipel_engine_t* e, int num_pa
 ASD_API size_t asd_mavipel_state_bytes(const asd_mavipel_engine_t* e, int max_seqs);
 ASD_API int asd_mavipel_set_cache(asd_mavipel_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
                                   int max_seqs, int max_pages_per_seq, float* state);
-/* options: "tc_linear", "tc_min_rows" as for the Mezilix engine; "profile" */
+/* options: "tc_linear", "tc_min_rows" as for the Mezilix engine; "attn_mma" (1, default: prompts and portions of a bf16
+ * engine take the tensor-core window attention where the sizes allow; 0: always the CUDA-core kernel); "profile" */
 ASD_API int asd_mavipel_set_option(asd_mavipel_engine_t* e, const char* name, int value);
 /* Same arguments as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
  * stream that leaves every layer execution. */

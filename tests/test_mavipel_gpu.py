@@ -447,6 +447,30 @@ def test_far_key_among_hundreds_without_a_mask_and_first_tokens():
         close(eng)
 
 
+def test_both_window_attention_kernels_agree():
+    """bf16 cache rows: the tensor-core kernel (weights as two bf16 terms) and the CUDA-core kernel read the same cache
+    and the same rounded queries, so they differ by fp32 roundings only; both stay within bf16's reach of the oracle.
+    Every value size the tensor-core kernel takes, one and several query heads per key/value head, windows shorter and
+    longer than a key tile, prompts, portions that end inside a query tile and single tokens"""
+    for heads, kv_heads, dim, vdim, size in ((4, 4, 32, 16, 100), (6, 2, 16, 32, 37), (8, 1, 64, 128, 130), (16, 4, 48, 64, 1000),
+                                             (3, 1, 80, 32, 7)):
+        cfg = config([par(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, size=size, rot_dims=16, scale=0.3, softcap=15.0)])
+        w = O.random_model(cfg, seed=55)
+        w["l0.mix.left.sink"] = torch.linspace(-2.0, 4.0, heads).to(torch.bfloat16)
+        ids = tokens(330, 120, 56)
+        ref = oracle(cfg, w, ids)
+        for cuts in ([330], [200, 64, 9, 1, 1, 2, 53], [300] + [1] * 30, [17] * 20):
+            got = []
+            for mma in (1, 0):
+                eng = make_engine(cfg, w, dtype=torch.bfloat16, max_tokens=512, max_seq_len=512, page_size=8)
+                eng.set_option("attn_mma", mma)
+                slot = eng.open_sequence()
+                got.append(feed(eng, slot, ids, cuts))
+                close(eng)
+                assert rel_err(got[-1], ref)[0] < 5e-2, (heads, kv_heads, cuts, mma)
+            assert rel_err(got[0], got[1].cpu())[0] < 2e-3, (heads, kv_heads, cuts)
+
+
 def test_single_token_steps_with_key_shares_over_several_ctas():
     """a long window and few sequences: single-token steps (and portions of two) cut the key tiles into shares for
     several CTAs and merge them, with the sink entering once, after the merge; two sequences of unequal length"""
