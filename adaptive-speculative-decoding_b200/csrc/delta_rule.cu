@@ -43,11 +43,11 @@ __global__ void __launch_bounds__(LC_CH) lowrank_channels_kernel(const float* a,
     const int nt = min(LC_TOK, M - m0);
     for (int i = threadIdx.x; i < LC_CH * p.low; i += LC_CH) {
         const int c = i / p.low, r = i - c * p.low;
-        wT[r * LC_CH + c] = c0 + c < n ? p.w2[(long long)(c0 + c) * p.low + r] : 0.f;
+        wT[r * LC_CH + c] = c0 + c < n ? __ldg(p.w2 + (long long)(c0 + c) * p.low + r) : 0.f;
     }
     for (int i = threadIdx.x; i < LC_TOK * p.low; i += LC_CH) {
         const int t = i / p.low, r = i - t * p.low;
-        float v = t < nt ? a[(long long)(m0 + t) * lda + r] : 0.f;
+        float v = t < nt ? __ldg(a + (long long)(m0 + t) * lda + r) : 0.f;
         if (p.inner_tanh) v = tanhf(v);
         av[i] = v;
     }
@@ -94,18 +94,18 @@ __global__ void short_conv_kernel(SeqIndex ix, const float* in, long long ld, co
     while (above < n - 1 && m - above - 1 >= 0 && ix.token_slot[m - above - 1] == slot &&
            ix.positions[m - above - 1] == pos - above - 1)
         ++above;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.f;
-        for (int j = 0; j < n; ++j) {
-            const int back = n - 1 - j;       // taps' last column weighs the current position
-            const int p = pos - back;
-            if (p < 0) continue;
-            const float v = back <= above ? in[(long long)(m - back) * ld + c]
-                                          : ring[((long long)slot * ring_n + p % ring_n) * C + c];
-            acc = fmaf(taps[(long long)c * n + j], v, acc);
-        }
-        out[(long long)m * C + c] = acc / (1.f + expf(-acc));
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;       // a channel per thread
+    if (c >= C) return;
+    float acc = 0.f;
+    for (int j = 0; j < n; ++j) {
+        const int back = n - 1 - j;       // taps' last column weighs the current position
+        const int p = pos - back;
+        if (p < 0) continue;
+        const float v = back <= above ? __ldg(in + (long long)(m - back) * ld + c)
+                                      : __ldg(ring + ((long long)slot * ring_n + p % ring_n) * C + c);
+        acc = fmaf(__ldg(taps + (long long)c * n + j), v, acc);
     }
+    out[(long long)m * C + c] = acc / (1.f + expf(-acc));
 }
 
 // the last ring_n new positions of every sequence leave their inputs behind (runs after short_conv_kernel has read)
@@ -325,6 +325,134 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
     }
 }
 
+// Key sizes up to 128: PARTS neighbouring lanes share a value column, each holding 32 key rows of it in registers, so
+// that the two dot products are closed by shuffles among those lanes and a position costs no barrier: the warps of a
+// CTA (one per 32 / PARTS columns of one (sequence, head)) only meet when a chunk of staged positions is used up.
+template <int PARTS, int NV>
+__global__ void __launch_bounds__(512, 1) delta_recurrence_cols_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
+                                                                       const float* rv, const float* sc, const float* v,
+                                                                       long long ldv, int heads, int dk, int dv, float* state,
+                                                                       int ring, float* out, int CH) {
+    constexpr int ROWS = 32, PS = 36, DKP = PS * PARTS;   // a row block's staged floats start PS apart: the blocks'
+                                                           // 16-byte reads fall into different banks
+    extern __shared__ __align__(16) float sm[];
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int t0 = cu_q[seq], t1 = cu_q[seq + 1];
+    if (t0 >= t1) return;
+    const int nthr = blockDim.x, dvp = nthr / PARTS;     // value columns padded to whole warps
+    const int col = threadIdx.x / PARTS, part = threadIdx.x % PARTS, r0 = part * ROWS;
+    const bool col_ok = col < dv;
+    const int slot = seq_slot[seq];
+    const int p0 = ix.positions[t0];
+    // shared: two buffers of { vectors [CH][NV][DKP], v [CH][dvp], scalars [CH][4] }
+    const int buf_elems = CH * NV * DKP + CH * dvp + CH * 4;
+    for (int i = threadIdx.x; i < 2 * buf_elems; i += nthr) sm[i] = 0.f;   // key rows beyond dk stay zero for good
+    const long long st_head = ((long long)head * dk) * dv;
+    const long long st_entry = (long long)heads * dk * dv;
+    float* st_slot = state + (long long)slot * ring * st_entry;
+    float S[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) S[r] = 0.f;
+    if (p0 > 0 && col_ok) {
+        const float* src = st_slot + (long long)((p0 - 1) % ring) * st_entry + st_head;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            if (r0 + r < dk) S[r] = src[(long long)(r0 + r) * dv + col];
+    }
+    const int hv = head * dv;
+    const bool v16 = (dk & 3) == 0;
+    __syncthreads();
+    auto fetch = [&](int buf, int c0) {
+        const int nt = min(CH, t1 - c0);
+        float* vec = sm + buf * buf_elems;
+        float* vs = vec + CH * NV * DKP;
+        float* ss = vs + CH * dvp;
+        if (v16) {
+            const int n4 = dk >> 2, per = NV * n4;
+            for (int i = threadIdx.x; i < nt * per; i += nthr) {
+                const int t = i / per, rest = i - t * per;
+                const int j = rest / n4, c4 = rest - j * n4;
+                cp_async16(vec + (t * NV + j) * DKP + (c4 >> 3) * PS + 4 * (c4 & 7), rv + (((long long)(c0 + t) * heads + head) * NV + j) * dk + 4 * c4);
+            }
+        } else {
+            const int per = NV * dk;
+            for (int i = threadIdx.x; i < nt * per; i += nthr) {
+                const int t = i / per, rest = i - t * per;
+                const int j = rest / dk, c = rest - j * dk;
+                cp_async4z(vec + (t * NV + j) * DKP + (c >> 5) * PS + (c & 31), rv + (((long long)(c0 + t) * heads + head) * NV + j) * dk + c, true);
+            }
+        }
+        for (int i = threadIdx.x; i < nt * dvp; i += nthr) {
+            const int t = i / dvp, c = i - t * dvp;
+            const bool ok = c < dv;
+            cp_async4z(vs + i, v + (ok ? (long long)(c0 + t) * ldv + hv + c : 0), ok);
+        }
+        for (int i = threadIdx.x; i < nt * 4; i += nthr)
+            cp_async4z(ss + i, sc + ((long long)(c0 + (i >> 2)) * heads + head) * 4 + (i & 3), true);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, t0);
+    int it = 0;
+    for (int c0 = t0; c0 < t1; c0 += CH, ++it) {
+        const int nt = min(CH, t1 - c0);
+        if (c0 + CH < t1) {
+            fetch((it + 1) & 1, c0 + CH);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();   // this chunk's rows have landed for every thread
+        const float* vec = sm + (it & 1) * buf_elems;
+        const float* vs = vec + CH * NV * DKP;
+        const float* ss = vs + CH * dvp;
+        for (int t = 0; t < nt; ++t) {
+            const float4* d4 = reinterpret_cast<const float4*>(vec + t * NV * DKP + part * PS);
+            const float4* x14 = d4 + DKP / 4;
+            const float4* x24 = d4 + 2 * (DKP / 4);
+            const float4* k4 = d4 + 3 * (DKP / 4);
+            const float4* y4 = d4 + (NV == 5 ? 4 : 3) * (DKP / 4);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+#pragma unroll
+            for (int r = 0; r < ROWS; r += 4) {
+                const float4 x = x14[r >> 2], z = x24[r >> 2];
+                a0 = fmaf(S[r], x.x, a0);
+                a1 = fmaf(S[r + 1], x.y, a1);
+                a2 = fmaf(S[r + 2], x.z, a2);
+                a3 = fmaf(S[r + 3], x.w, a3);
+                b0 = fmaf(S[r], z.x, b0);
+                b1 = fmaf(S[r + 1], z.y, b1);
+                b2 = fmaf(S[r + 2], z.z, b2);
+                b3 = fmaf(S[r + 3], z.w, b3);
+            }
+            float A = (a0 + a1) + (a2 + a3), B = (b0 + b1) + (b2 + b3);
+#pragma unroll
+            for (int o = 1; o < PARTS; o <<= 1) {       // the column's other row blocks: the same total in every lane
+                A += __shfl_xor_sync(0xffffffffu, A, o);
+                B += __shfl_xor_sync(0xffffffffu, B, o);
+            }
+            const float vv = vs[t * dvp + col];
+            const float cA = -ss[t * 4 + 0] * A, cB = ss[t * 4 + 1] * vv;
+#pragma unroll
+            for (int r = 0; r < ROWS; r += 4) {
+                const float4 dd = d4[r >> 2], kk = k4[r >> 2], yy = y4[r >> 2];
+                S[r] = fmaf(kk.x, cB, fmaf(yy.x, cA, dd.x * S[r]));
+                S[r + 1] = fmaf(kk.y, cB, fmaf(yy.y, cA, dd.y * S[r + 1]));
+                S[r + 2] = fmaf(kk.z, cB, fmaf(yy.z, cA, dd.z * S[r + 2]));
+                S[r + 3] = fmaf(kk.w, cB, fmaf(yy.w, cA, dd.w * S[r + 3]));
+            }
+            const int m = c0 + t;
+            if (col_ok && part == 0) out[(long long)m * heads * dv + hv + col] = fmaf(cB, ss[t * 4 + 3], fmaf(cA, ss[t * 4 + 2], B));
+            if (t1 - m <= ring && col_ok) {     // the last `ring` new positions leave their state behind
+                float* dst = st_slot + (long long)((p0 + (m - t0)) % ring) * st_entry + st_head;
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    if (r0 + r < dk) dst[(long long)(r0 + r) * dv + col] = S[r];
+            }
+        }
+        __syncthreads();   // the chunk is consumed: its buffer may be refilled
+    }
+}
+
 // ------------------------------------------------------------------------------------------ norm and gate of the result
 // one warp per (token, head): y = o / rms(o over dv) * w * gate * scale
 __global__ void head_norm_gate_kernel(const float* o, HeadNormGate p, void* y, int of32, long long ldy, int heads, int dv) {
@@ -370,7 +498,10 @@ int launch_short_conv(const SeqIndex& ix, const float* in, long long ld, const f
     if (ix.M <= 0 || C <= 0) return 0;
     if (n_taps <= 0 || (n_taps > 1 && (!ring || ring_n < n_taps - 1)))
         return set_error("short_conv: %d taps need a ring of at least %d carried inputs", n_taps, n_taps - 1);
-    short_conv_kernel<<<ix.M, C >= 1024 ? 256 : 128, 0, stream>>>(ix, in, ld, taps, n_taps, C, ring, ring_n > 0 ? ring_n : 1, out);
+    const int threads = C >= 1024 ? 256 : 128;
+    dim3 grid(ix.M, (C + threads - 1) / threads);
+    if (grid.y > 65535) return set_error("short_conv: too many channels");
+    short_conv_kernel<<<grid, threads, 0, stream>>>(ix, in, ld, taps, n_taps, C, ring, ring_n > 0 ? ring_n : 1, out);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
@@ -404,8 +535,42 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     if (ix.M <= 0 || nseq <= 0) return 0;
     if (dk <= 0 || dk > 1024) return set_error("delta rule: key size %d outside 1..1024", dk);
     if (ring <= 0 || !state) return set_error("delta rule: no state");
+    const int parts = dk <= 32 ? 1 : (dk <= 64 ? 2 : 4);
+    // steps of single tokens: the state is read and written once per position and the shuffle form keeps more loads in
+    // flight; prompts and portions: the slices over warps read every staged vector once per warp as a broadcast
+    if (ix.M <= 2 * nseq && dk <= 128 && ((dv + 32 / parts - 1) / (32 / parts)) * 32 <= 512) {   // row blocks closed by shuffles: no barrier per position
+        const int nvv = general ? 5 : 4, dkp = 36 * parts;
+        const int cpw = 32 / parts, warps = (dv + cpw - 1) / cpw, dvp = warps * cpw;
+        int ch = 16;
+        auto need = [&](int c) { return (size_t)(2 * (c * nvv * dkp + c * dvp + c * 4)) * sizeof(float); };
+        while (ch > 1 && need(ch) > 100 * 1024) ch >>= 1;
+        dim3 grid(nseq, heads);
+        if (grid.y > 65535) return set_error("delta rule: too many heads");
+#define ASD_DC_CASE(P_, NVV)                                                                                           \
+    {                                                                                                                 \
+        auto fn = delta_recurrence_cols_kernel<P_, NVV>;                                                              \
+        static PerDeviceOnce once;                                                                                    \
+        if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+        fn<<<grid, warps * 32, need(ch), stream>>>(ix, cu_q, seq_slot, rv, sc, v, ldv, heads, dk, dv, state, ring, out, \
+                                                   ch);                                                               \
+    }
+#define ASD_DC_PARTS(NVV)                        \
+    if (parts == 1) ASD_DC_CASE(1, NVV)          \
+    else if (parts == 2) ASD_DC_CASE(2, NVV)     \
+    else ASD_DC_CASE(4, NVV)
+        if (general) {
+            ASD_DC_PARTS(5)
+        } else {
+            ASD_DC_PARTS(4)
+        }
+#undef ASD_DC_PARTS
+#undef ASD_DC_CASE
+        count_launch(1);
+        ASD_CUDA(cudaGetLastError());
+        return 0;
+    }
     int rows = 4;
-    while (rows < 32 && rows * 8 < dk) rows *= 2;
+    while (rows < 32 && rows * 4 < dk) rows *= 2;     // four warps up to key size 128, then more
     const int RS = (dk + rows - 1) / rows;
     const int dkp = RS * rows, nv = general ? 5 : 4;
     int ch = 16;   // positions per staged chunk: as many as two buffers of a head's vectors leave room for

@@ -26,7 +26,7 @@ __global__ void embed_scaled_kernel(SeqIndex ix, const void* embed, int wf32, fl
     }
 }
 
-constexpr int MAX_NORM_GROUPS = 16;   // parts a grouped norm may split a row into
+constexpr int MAX_NORM_GROUPS = 64;   // parts a grouped norm may split a row into
 
 // dynamic shared memory: D floats (the row being built) + 33 for the block sums + MAX_NORM_GROUPS group factors
 __global__ void row_close_kernel(RowClose c) {

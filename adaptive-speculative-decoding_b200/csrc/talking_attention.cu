@@ -484,6 +484,138 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
     }
 }
 
+// ---------------------------------------------------------------------------------------------- steps of few tokens
+// One CTA per (token, share of its key tiles), one warp per head, nothing staged: lane = key reads its own cache row in
+// 16-byte pieces (several in flight) against the query in shared memory; the capped scores go to shared memory (two
+// buffers, one barrier per tile); every warp mixes its head's row, updates the running softmax and adds the values with
+// each lane on four neighbouring value columns, the rows' addresses passed from lane to lane.  Small shared memory and
+// few registers: several CTAs share an SM and hide one another's loads.
+template <typename T>
+__global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const float* q, long long ldq, TalkDims d,
+                                                              const float* talk, const float* sink, PagedRows cache, void* out,
+                                                              int of32, long long ldo, float out_scale, float* part, int nsplit) {
+    constexpr int VE = 16 / sizeof(T);
+    extern __shared__ __align__(16) float sm[];
+    const int m = blockIdx.x;
+    const int H = d.heads, G = d.kv_heads, dk = d.dk, dv = d.dv;
+    const int lane = threadIdx.x & 31, h = threadIdx.x >> 5, nthr = blockDim.x;
+    const int kvh = h / (H / G);
+    const int slot = ix.token_slot[m], pos = ix.positions[m];
+    float* qs = sm;                        // [H][dk]
+    float* Ss = qs + ((H * dk + 3) & ~3);  // [2][H][32]
+    float* Ps = Ss + 2 * H * 32;           // [H][32]
+    float* Ts = Ps + H * 32;               // [H][H]
+    for (int i = threadIdx.x; i < H * dk; i += nthr) {
+        float qv = q[(long long)m * ldq + i];
+        if (sizeof(T) == 2) qv = __bfloat162float(__float2bfloat16(qv));
+        qs[i] = qv;
+    }
+    for (int i = threadIdx.x; i < H * H; i += nthr) Ts[i] = talk ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+    const bool whole = nsplit <= 1;
+    float mx = sink && whole ? sink[h] : -INFINITY, sum = sink && whole ? 1.f : 0.f;
+    float O[2][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a) O[a][0] = O[a][1] = O[a][2] = O[a][3] = 0.f;
+    const int lo_pos = max(0, pos - d.window + 1);
+    int kt_lo = lo_pos / 32, kt_hi = pos / 32;
+    if (!whole) {
+        const int per = (kt_hi - kt_lo + nsplit) / nsplit;
+        kt_lo += blockIdx.y * per;
+        kt_hi = min(kt_hi, kt_lo + per - 1);
+    }
+    const int nk = G * dk, row_elems = nk + G * dv;
+    const T* pool = static_cast<const T*>(cache.pool);
+    const float* qh = qs + h * dk;
+    const int groups = dv >> 2;            // four value columns per lane and group
+    __syncthreads();
+    int par = 0;
+    for (int kt = kt_lo; kt <= kt_hi; ++kt, par ^= 1) {
+        const int j = kt * 32 + lane;
+        const bool ok = j >= lo_pos && j <= pos;
+        const long long row = ok ? cache_row(cache, slot, j) * row_elems : 0;
+        float s = 0.f;
+        if (ok) {
+            const uint4* kp = reinterpret_cast<const uint4*>(pool + row + kvh * dk);
+            float s0 = 0.f, s1 = 0.f;
+            for (int c0 = 0; c0 < dk; c0 += 8 * VE) {
+                uint4 r[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) r[u] = c0 + u * VE < dk ? __ldg(kp + c0 / VE + u) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (c0 + u * VE >= dk) continue;
+                    const T* x = reinterpret_cast<const T*>(&r[u]);
+                    const float* qc = qh + c0 + u * VE;
+#pragma unroll
+                    for (int i = 0; i < VE; i += 2) {
+                        s0 = fmaf(qc[i], (float)x[i], s0);
+                        s1 = fmaf(qc[i + 1], (float)x[i + 1], s1);
+                    }
+                }
+            }
+            s = (s0 + s1) * d.scale;
+            if (d.softcap > 0.f) s = d.softcap * tanhf(s / d.softcap);
+        }
+        float* sb = Ss + par * H * 32;
+        sb[h * 32 + lane] = s;
+        __syncthreads();
+        float mixed = 0.f;
+        for (int g = 0; g < H; ++g) mixed = fmaf(Ts[h * H + g], sb[g * 32 + lane], mixed);
+        const float m_new = fmaxf(mx, warp_max(ok ? mixed : -INFINITY));
+        const float p = ok ? expf(mixed - m_new) : 0.f;
+        const float corr = mx == -INFINITY ? 0.f : expf(mx - m_new);
+        sum = sum * corr + warp_sum(p);
+        mx = m_new;
+#pragma unroll
+        for (int a = 0; a < 2; ++a) O[a][0] *= corr, O[a][1] *= corr, O[a][2] *= corr, O[a][3] *= corr;
+        const long long vrow = row + nk + kvh * dv;
+        // no branch on a zero weight: the loads of eight keys stay in flight together (a masked key's row is row 0 of
+        // the pool, readable and multiplied by zero)
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float pk = __shfl_sync(0xffffffffu, p, k);
+            const long long vr = __shfl_sync(0xffffffffu, vrow, k);
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+                const int gi = lane + 32 * a;
+                if (gi < groups) {
+                    float v0, v1, v2, v3;
+                    if (sizeof(T) == 2) {
+                        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(pool + vr + 4 * gi));
+                        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                        v0 = __bfloat162float(lo.x), v1 = __bfloat162float(lo.y), v2 = __bfloat162float(hi.x), v3 = __bfloat162float(hi.y);
+                    } else {
+                        const float4 raw = __ldg(reinterpret_cast<const float4*>(pool + vr + 4 * gi));
+                        v0 = raw.x, v1 = raw.y, v2 = raw.z, v3 = raw.w;
+                    }
+                    O[a][0] = fmaf(pk, v0, O[a][0]);
+                    O[a][1] = fmaf(pk, v1, O[a][1]);
+                    O[a][2] = fmaf(pk, v2, O[a][2]);
+                    O[a][3] = fmaf(pk, v3, O[a][3]);
+                }
+            }
+        }
+    }
+    if (!whole) {
+        float* dst = part + (((long long)m * nsplit + blockIdx.y) * H + h) * (dv + 2);
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+            if (lane + 32 * a < groups)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[4 * (lane + 32 * a) + i] = O[a][i];
+        if (lane == 0) dst[dv] = mx, dst[dv + 1] = sum;
+        return;
+    }
+    const float r = out_scale / sum;
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+        if (lane + 32 * a < groups)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                stx(out, (long long)m * ldo + (long long)h * dv + 4 * (lane + 32 * a) + i, of32, O[a][i] * r);
+}
+
 // one warp per (token, head): the shares' sums brought to a common maximum, the sink entering once
 __global__ void talk_merge_kernel(const float* part, int nsplit, const float* sink, void* out, int of32, long long ldo,
                                   float out_scale, int M, int H, int dv) {
@@ -493,21 +625,22 @@ __global__ void talk_merge_kernel(const float* part, int nsplit, const float* si
     const int m = (int)(idx / H), h = (int)(idx - (long long)m * H);
     const float* base = part + ((long long)m * nsplit * H + h) * (dv + 2);
     const long long step = (long long)H * (dv + 2);
-    float top = sink ? sink[h] : -INFINITY;
-    for (int s = 0; s < nsplit; ++s) top = fmaxf(top, base[s * step + dv]);
-    float den = sink ? expf(sink[h] - top) : 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float ms = base[s * step + dv];
-        if (ms != -INFINITY) den += base[s * step + dv + 1] * expf(ms - top);
-    }
+    // lane = share (at most 32): its maximum and denominator, brought to the common maximum
+    const float ms = lane < nsplit ? __ldg(base + lane * step + dv) : -INFINITY;
+    const float ls = lane < nsplit ? __ldg(base + lane * step + dv + 1) : 0.f;
+    const float top = fmaxf(sink ? sink[h] : -INFINITY, warp_max(ms));
+    const float ws = ms == -INFINITY ? 0.f : expf(ms - top);
+    const float den = warp_sum(ls * ws) + (sink ? expf(sink[h] - top) : 0.f);
     const float r = out_scale / den;
-    for (int c = lane; c < dv; c += 32) {
+    for (int c0 = 0; c0 < dv; c0 += 32) {
+        const int c = c0 + lane;
         float o = 0.f;
+#pragma unroll 8
         for (int s = 0; s < nsplit; ++s) {
-            const float ms = base[s * step + dv];
-            if (ms != -INFINITY) o = fmaf(base[s * step + c], expf(ms - top), o);
+            const float w = __shfl_sync(0xffffffffu, ws, s);
+            o = fmaf(c < dv ? __ldg(base + s * step + c) : 0.f, w, o);
         }
-        stx(out, (long long)m * ldo + (long long)h * dv + c, of32, o * r);
+        if (c < dv) stx(out, (long long)m * ldo + (long long)h * dv + c, of32, o * r);
     }
 }
 
@@ -559,6 +692,47 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
             return 0;
         }
     }
+    // steps of few tokens: a CTA per (token, share of its key tiles), rows read straight from the cache
+    {
+        const int ve = cache.f32 ? 4 : 8;
+        if (ws.tiled && max_qlen < 8 && d.dk % ve == 0 && d.dv % 4 == 0 && (d.kv_heads * d.dv) % ve == 0 &&
+            (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0) {
+            const int tiles = (int)((long long)(d.window < max_kv_len ? d.window : max_kv_len) + 31) / 32 + 1;
+            int nsplit = 1;
+            if (ws.o && tiles >= 4) {
+                nsplit = (int)((148 * 4 + ix.M - 1) / ix.M);
+                if (nsplit > tiles / 2) nsplit = tiles / 2;
+                if (nsplit > 32) nsplit = 32;
+                const long long per_share = (long long)ix.M * d.heads * (d.dv + 2);
+                if ((long long)nsplit * per_share > ws.o_elems) nsplit = (int)(ws.o_elems / per_share);
+                if (nsplit < 2) nsplit = 1;
+            }
+            const size_t smem = (size_t)(((d.heads * d.dk + 3) & ~3) + 3 * d.heads * 32 + d.heads * d.heads) * sizeof(float);
+            dim3 grid(ix.M, nsplit);
+            if (smem <= 200 * 1024 && nsplit <= 65535) {
+                static PerDeviceOnce once;
+                if (once.need()) {
+                    ASD_CUDA(cudaFuncSetAttribute(talk_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+                    ASD_CUDA(cudaFuncSetAttribute(talk_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+                }
+                if (cache.f32)
+                    talk_decode_kernel<float><<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out, of32, ldo,
+                                                                                   out_scale, ws.o, nsplit);
+                else
+                    talk_decode_kernel<__nv_bfloat16><<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out,
+                                                                                           of32, ldo, out_scale, ws.o, nsplit);
+                count_launch(1);
+                if (nsplit > 1) {
+                    const long long warps = (long long)ix.M * d.heads;
+                    talk_merge_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(ws.o, nsplit, sink, out, of32, ldo, out_scale,
+                                                                                     ix.M, d.heads, d.dv);
+                    count_launch(1);
+                }
+                ASD_CUDA(cudaGetLastError());
+                return 0;
+            }
+        }
+    }
     // Key tile and query tile from the layer's sizes (the key tile never depends on the batch: a position's sums run over
     // the same tiles whatever it is fed with); single-token steps take one query position per CTA.
     const int esz = cache.f32 ? 4 : 2, ve = 16 / esz;
@@ -585,6 +759,7 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
     if (ws.o && ctas * 2 <= 148 && tiles >= 4) {
         nsplit = (int)(148 / ctas);
         if (nsplit > tiles / 2) nsplit = tiles / 2;
+        if (nsplit > 32) nsplit = 32;
         const long long per_share = (long long)ix.M * d.heads * (d.dv + 2);
         if ((long long)nsplit * per_share > ws.o_elems) nsplit = (int)(ws.o_elems / per_share);
         if (nsplit < 2) nsplit = 1;
