@@ -324,7 +324,8 @@ int launch_talk_post(const SeqIndex& ix, float* qkv, long long ld, const TalkDim
                      const float* k_norm, float eps, const float* freq, const PagedRows& cache, cudaStream_t stream);
 // out[m][h][:] (rows ldo apart, engine's element type) = out_scale * sum_j p[h][j] v[j]; talk fp32 [heads][heads]
 // (nullptr: no mixing), sink fp32 [heads] (nullptr: none).  ws.o (o_elems floats; may be nullptr) holds the partial
-// results when steps of few tokens cut the key tiles into shares for several CTAs.
+// results when steps of few tokens cut the key tiles into shares for several CTAs; ws.ml (optional: `rows` zeroed
+// 32-bit counters, one per token) lets a token's last CTA to arrive merge them instead of a kernel of its own.
 int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
                           const float* q, long long ldq, const TalkDims& d, const float* talk, const float* sink,
                           const PagedRows& cache, void* out, int of32, long long ldo, float out_scale, const AttnSplit& ws,

@@ -499,7 +499,12 @@ asd_mavipel_engine_t* asd_mavipel_create(const asd_mavipel_config* cfg, const as
     rc |= dev_alloc(e, &e->slot_of, MT * top);
     // key shares are used while CTAs are fewer than half the SMs: at most 148 x 8 (token, share) pairs
     e->attn_ws.o_elems = (long long)(148 * 8 * share);
-    if (share) rc |= dev_alloc(e, &e->attn_ws.o, (size_t)e->attn_ws.o_elems);
+    if (share) {
+        rc |= dev_alloc(e, &e->attn_ws.o, (size_t)e->attn_ws.o_elems);
+        rc |= dev_alloc(e, &e->attn_ws.ml, MT);      // arrival counters of the key shares, one per token
+        e->attn_ws.rows = (long long)MT;
+        if (!rc && cudaMemset(e->attn_ws.ml, 0, MT * sizeof(float)) != cudaSuccess) rc = -1;
+    }
     rc |= dev_alloc(e, &e->dev_error, 1);
     if (!rc && cudaMemset(e->dev_error, 0, sizeof(int)) != cudaSuccess) rc = -1;
     if (rc) {

@@ -290,43 +290,60 @@ __global__ void __launch_bounds__(TQ > 2 ? 512 : 1024, 1) talk_attention_kernel(
 // weights, as two bf16 terms (value + residual), with the values; barrier; the next tile's values start to arrive.
 constexpr int TM_TK = 32, TM_TQ = 16, TM_SS = 40;   // key tile, query tile, floats per score row (32 + padding)
 
-template <int NDV>   // value size / 8
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// NDV = value size / 8.  PAIR: 17 to 32 heads run as a cluster of two CTAs with half of the heads each; a CTA computes
+// its heads' scores and writes them into BOTH CTAs' shared memory (distributed shared memory), so that each can mix
+// its heads' rows from all heads; two cluster barriers per tile take the place of two CTA barriers.  Both CTAs of a
+// pair serve the same query tile, so they run the same number of tiles and meet at every barrier.
+template <int NDV, bool PAIR>
 __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
                                                                     const float* q, long long ldq, TalkDims d,
                                                                     const float* talk, const float* sink, PagedRows cache,
                                                                     void* out, int of32, long long ldo, float out_scale) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int seq = blockIdx.y;
-    const int t0 = cu_q[seq] + blockIdx.x * TM_TQ, t1 = min(cu_q[seq + 1], t0 + TM_TQ);
-    if (t0 >= t1) return;
+    const int z = PAIR ? (int)(blockIdx.x & 1) : 0;                  // rank in the pair
+    const int t0 = cu_q[seq] + (PAIR ? blockIdx.x >> 1 : blockIdx.x) * TM_TQ, t1 = min(cu_q[seq + 1], t0 + TM_TQ);
+    if (t0 >= t1) return;                                            // the same for both CTAs of a pair
     const int nq = t1 - t0;
     const int H = d.heads, G = d.kv_heads, dk = d.dk;
+    const int Hc = PAIR ? H / 2 : H;                                 // heads of this CTA: z * Hc ...
     constexpr int dv = NDV * 8;
-    const int lane = threadIdx.x & 31, h = threadIdx.x >> 5, nthr = blockDim.x;
-    const int kvh = h / (H / G);
+    const int lane = threadIdx.x & 31, hl = threadIdx.x >> 5, nthr = blockDim.x;
+    const int h = z * Hc + hl;                                       // this warp's head
+    const int g_lo = (z * Hc) / (H / G), g_hi = (z * Hc + Hc - 1) / (H / G), Gc = g_hi - g_lo + 1;   // key/value heads staged
+    const int kvh = h / (H / G) - g_lo;
     const int slot = seq_slot[seq];
     const int pos0 = ix.positions[t0], pos1 = pos0 + nq - 1;
-    const int qstride = H * dk + 8, kstride = G * dk + 8, vstride = G * dv + 8;     // bf16 elements; rows 16 bytes apart mod 128
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [16][qstride]
+    const int qstride = Hc * dk + 8, kstride = Gc * dk + 8, vstride = Gc * dv + 8;  // bf16 elements; rows 16 bytes apart mod 128
+    // the scores come first: their place must be the same in both CTAs of a pair, whatever the other sizes
+    float* Ss = reinterpret_cast<float*>(smraw);                                  // [H][16][TM_SS]
+    float* Ts = Ss + H * TM_TQ * TM_SS;                                           // [Hc][H]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(Ts + ((Hc * H + 3) & ~3));   // [16][qstride]
     __nv_bfloat16* Ks = Qs + TM_TQ * qstride;                                     // [32][kstride]
     __nv_bfloat16* Vs = Ks + TM_TK * kstride;                                     // [32][vstride]
-    float* Ss = reinterpret_cast<float*>(Vs + TM_TK * vstride);                   // [H][16][TM_SS]
-    float* Ts = Ss + H * TM_TQ * TM_SS;                                           // [H][H]
-    for (int i = threadIdx.x; i < TM_TQ * H * dk; i += nthr) {
-        const int t = i / (H * dk), c = i - t * (H * dk);
-        Qs[t * qstride + c] = __float2bfloat16(t < nq ? q[(long long)(t0 + t) * ldq + c] : 0.f);
+    for (int i = threadIdx.x; i < TM_TQ * Hc * dk; i += nthr) {
+        const int t = i / (Hc * dk), c = i - t * (Hc * dk);
+        Qs[t * qstride + c] = __float2bfloat16(t < nq ? q[(long long)(t0 + t) * ldq + z * Hc * dk + c] : 0.f);
     }
-    for (int i = threadIdx.x; i < H * H; i += nthr) Ts[i] = talk ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
-    const int nk = G * dk, nv = G * dv, row_elems = nk + nv;
+    for (int i = threadIdx.x; i < Hc * H; i += nthr) {
+        const int row = z * Hc + i / H, col = i % H;
+        Ts[i] = talk ? talk[row * H + col] : (row == col ? 1.f : 0.f);
+    }
+    const int nk = G * dk, row_elems = nk + G * dv;
     const __nv_bfloat16* pool = static_cast<const __nv_bfloat16*>(cache.pool);
-    const int kvec = nk / 8, vvec = nv / 8;
+    const int kvec = Gc * dk / 8, vvec = Gc * dv / 8;
+    const int koff = g_lo * dk, voff = nk + g_lo * dv;                 // this CTA's key / value heads within a cache row
     auto fetch_k = [&](int kt) {
         if (kt >= 0) {
             for (int i = threadIdx.x; i < TM_TK * kvec; i += nthr) {
                 const int t = i / kvec, c = i - t * kvec;
                 const int j = kt * TM_TK + t;
                 const bool ok = j <= pos1;
-                const __nv_bfloat16* src = pool + (ok ? cache_row(cache, slot, j) * row_elems + c * 8 : 0);
+                const __nv_bfloat16* src = pool + (ok ? cache_row(cache, slot, j) * row_elems + koff + c * 8 : 0);
                 cp_async16((uint32_t)__cvta_generic_to_shared(Ks + t * kstride + c * 8), src, ok);
             }
         }
@@ -338,7 +355,7 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
                 const int t = i / vvec, c = i - t * vvec;
                 const int j = kt * TM_TK + t;
                 const bool ok = j <= pos1;
-                const __nv_bfloat16* src = pool + (ok ? cache_row(cache, slot, j) * row_elems + nk + c * 8 : 0);
+                const __nv_bfloat16* src = pool + (ok ? cache_row(cache, slot, j) * row_elems + voff + c * 8 : 0);
                 cp_async16((uint32_t)__cvta_generic_to_shared(Vs + t * vstride + c * 8), src, ok);
             }
         }
@@ -353,7 +370,7 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
     const int kt_lo = max(0, pos0 - d.window + 1) / TM_TK, kt_hi = pos1 / TM_TK;
     fetch_k(kt_lo);
     fetch_v(kt_lo);
-    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (lane & 15) * qstride + h * dk + (lane >> 4) * 8);
+    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (lane & 15) * qstride + hl * dk + (lane >> 4) * 8);
     const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + ((lane & 7) + (lane >> 4) * 8) * kstride + kvh * dk + ((lane >> 3) & 1) * 8);
     const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * vstride + kvh * dv + (lane >> 4) * 8);
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
@@ -374,6 +391,11 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
             }
         }
         float* sh = Ss + (h * TM_TQ) * TM_SS;
+        uint32_t peer = 0;
+        if constexpr (PAIR) {
+            const uint32_t mine = (uint32_t)__cvta_generic_to_shared(sh);
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(mine), "r"(z ^ 1));
+        }
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
 #pragma unroll
@@ -382,15 +404,23 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
                 if (d.softcap > 0.f) v = d.softcap * tanhf(v / d.softcap);
                 acc[n][i] = v;
             }
-            *reinterpret_cast<float2*>(sh + gq * TM_SS + 8 * n + 2 * tq) = make_float2(acc[n][0], acc[n][1]);
-            *reinterpret_cast<float2*>(sh + (gq + 8) * TM_SS + 8 * n + 2 * tq) = make_float2(acc[n][2], acc[n][3]);
+            const int o0 = gq * TM_SS + 8 * n + 2 * tq, o1 = (gq + 8) * TM_SS + 8 * n + 2 * tq;
+            *reinterpret_cast<float2*>(sh + o0) = make_float2(acc[n][0], acc[n][1]);
+            *reinterpret_cast<float2*>(sh + o1) = make_float2(acc[n][2], acc[n][3]);
+            if constexpr (PAIR) {      // the same rows of the other CTA's copy
+                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(peer + o0 * 4), "f"(acc[n][0]), "f"(acc[n][1]) : "memory");
+                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(peer + o1 * 4), "f"(acc[n][2]), "f"(acc[n][3]) : "memory");
+            }
         }
-        __syncthreads();         // every head's scores are there; the key buffer is free
+        if constexpr (PAIR)
+            cluster_barrier();   // every head's scores are in both CTAs; the key buffer is free
+        else
+            __syncthreads();     // every head's scores are there; the key buffer is free
         fetch_k(kt < kt_hi ? kt + 1 : -1);
 #pragma unroll
         for (int n = 0; n < 4; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
         for (int g = 0; g < H; ++g) {
-            const float w = Ts[h * H + g];
+            const float w = Ts[hl * H + g];
             const float* sg = Ss + (g * TM_TQ) * TM_SS + 2 * tq;
 #pragma unroll
             for (int n = 0; n < 4; ++n) {
@@ -462,7 +492,10 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
                 mma_bf16(O[n + 1], pl, b[2], b[3]);
             }
         }
-        __syncthreads();         // the value buffer is free
+        if constexpr (PAIR)
+            cluster_barrier();   // the value buffer is free, and the other CTA is done reading this tile's scores
+        else
+            __syncthreads();     // the value buffer is free
         fetch_v(kt < kt_hi ? kt + 1 : -1);
     }
     cp_async_wait<0>();
@@ -484,6 +517,40 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
     }
 }
 
+// one warp per (token, head): the shares' sums brought to a common maximum, the sink entering once.  lane = share (at
+// most 32).  `fresh`: the partial results were written by other CTAs of the SAME launch (read past the L1 cache).
+template <bool FRESH>
+__device__ __forceinline__ void merge_shares(const float* base, long long step, int nsplit, const float* sink, int h, void* out,
+                                             int of32, long long orow, float out_scale, int dv, int lane) {
+    auto ld = [](const float* p) { return FRESH ? __ldcg(p) : __ldg(p); };
+    const float ms = lane < nsplit ? ld(base + lane * step + dv) : -INFINITY;
+    const float ls = lane < nsplit ? ld(base + lane * step + dv + 1) : 0.f;
+    const float top = fmaxf(sink ? sink[h] : -INFINITY, warp_max(ms));
+    const float ws = ms == -INFINITY ? 0.f : expf(ms - top);
+    const float den = warp_sum(ls * ws) + (sink ? expf(sink[h] - top) : 0.f);
+    const float r = out_scale / den;
+    for (int c0 = 0; c0 < dv; c0 += 32) {
+        const int c = c0 + lane;
+        float o = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < nsplit; ++s) {
+            const float w = __shfl_sync(0xffffffffu, ws, s);
+            o = fmaf(c < dv ? ld(base + s * step + c) : 0.f, w, o);
+        }
+        if (c < dv) stx(out, orow + c, of32, o * r);
+    }
+}
+
+__global__ void talk_merge_kernel(const float* part, int nsplit, const float* sink, void* out, int of32, long long ldo,
+                                  float out_scale, int M, int H, int dv) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (idx >= (long long)M * H) return;
+    const int m = (int)(idx / H), h = (int)(idx - (long long)m * H);
+    merge_shares<false>(part + ((long long)m * nsplit * H + h) * (dv + 2), (long long)H * (dv + 2), nsplit, sink, h, out, of32,
+                        (long long)m * ldo + (long long)h * dv, out_scale, dv, lane);
+}
+
 // ---------------------------------------------------------------------------------------------- steps of few tokens
 // One CTA per (token, share of its key tiles), one warp per head, nothing staged: lane = key reads its own cache row in
 // 16-byte pieces (several in flight) against the query in shared memory; the capped scores go to shared memory (two
@@ -493,7 +560,8 @@ __global__ void __launch_bounds__(512, 1) talk_attention_mma_kernel(SeqIndex ix,
 template <typename T>
 __global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const float* q, long long ldq, TalkDims d,
                                                               const float* talk, const float* sink, PagedRows cache, void* out,
-                                                              int of32, long long ldo, float out_scale, float* part, int nsplit) {
+                                                              int of32, long long ldo, float out_scale, float* part, int nsplit,
+                                                              int* arrived) {
     constexpr int VE = 16 / sizeof(T);
     extern __shared__ __align__(16) float sm[];
     const int m = blockIdx.x;
@@ -605,6 +673,21 @@ __global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dst[4 * (lane + 32 * a) + i] = O[a][i];
         if (lane == 0) dst[dv] = mx, dst[dv + 1] = sum;
+        if (!arrived) return;       // a kernel of its own merges
+        // the token's last CTA to arrive merges its shares (one launch less); it puts the counter back for the next step
+        __shared__ int last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int t = atomicAdd(arrived + m, 1);
+            last = t == nsplit - 1;
+            if (last) arrived[m] = 0;
+        }
+        __syncthreads();
+        if (!last) return;
+        __threadfence();
+        merge_shares<true>(part + ((long long)m * nsplit * H + h) * (dv + 2), (long long)H * (dv + 2), nsplit, sink, h, out, of32,
+                           (long long)m * ldo + (long long)h * dv, out_scale, dv, lane);
         return;
     }
     const float r = out_scale / sum;
@@ -614,34 +697,6 @@ __global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const
 #pragma unroll
             for (int i = 0; i < 4; ++i)
                 stx(out, (long long)m * ldo + (long long)h * dv + 4 * (lane + 32 * a) + i, of32, O[a][i] * r);
-}
-
-// one warp per (token, head): the shares' sums brought to a common maximum, the sink entering once
-__global__ void talk_merge_kernel(const float* part, int nsplit, const float* sink, void* out, int of32, long long ldo,
-                                  float out_scale, int M, int H, int dv) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (idx >= (long long)M * H) return;
-    const int m = (int)(idx / H), h = (int)(idx - (long long)m * H);
-    const float* base = part + ((long long)m * nsplit * H + h) * (dv + 2);
-    const long long step = (long long)H * (dv + 2);
-    // lane = share (at most 32): its maximum and denominator, brought to the common maximum
-    const float ms = lane < nsplit ? __ldg(base + lane * step + dv) : -INFINITY;
-    const float ls = lane < nsplit ? __ldg(base + lane * step + dv + 1) : 0.f;
-    const float top = fmaxf(sink ? sink[h] : -INFINITY, warp_max(ms));
-    const float ws = ms == -INFINITY ? 0.f : expf(ms - top);
-    const float den = warp_sum(ls * ws) + (sink ? expf(sink[h] - top) : 0.f);
-    const float r = out_scale / den;
-    for (int c0 = 0; c0 < dv; c0 += 32) {
-        const int c = c0 + lane;
-        float o = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < nsplit; ++s) {
-            const float w = __shfl_sync(0xffffffffu, ws, s);
-            o = fmaf(c < dv ? __ldg(base + s * step + c) : 0.f, w, o);
-        }
-        if (c < dv) stx(out, (long long)m * ldo + (long long)h * dv + c, of32, o * r);
-    }
 }
 
 }  // namespace
@@ -665,28 +720,47 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
     if (d.heads <= 0 || d.heads > 32 || d.kv_heads <= 0 || d.heads % d.kv_heads)
         return set_error("talk_attention: %d heads (at most 32) over %d key/value heads", d.heads, d.kv_heads);
     if (d.dv > 256 || d.dv <= 0 || d.dk <= 0 || d.window <= 0) return set_error("talk_attention: bad sizes");
-    // bf16 cache rows and sizes that fill the tensor-core fragments: prompts and portions take the mma.sync kernel
-    if (ws.tiled && !cache.f32 && max_qlen >= 8 && d.heads <= 16 && d.dk % 16 == 0 &&
+    // bf16 cache rows and sizes that fill the tensor-core fragments: prompts and portions take the mma.sync kernel, up to
+    // 16 heads in one CTA, 17 to 32 (an even number) in a cluster of two
+    if (ws.tiled && !cache.f32 && max_qlen >= 8 && d.heads <= 32 && (d.heads <= 16 || d.heads % 2 == 0) && d.dk % 16 == 0 &&
         (d.dv == 16 || d.dv == 32 || d.dv == 64 || d.dv == 128) && (reinterpret_cast<uintptr_t>(cache.pool) & 15) == 0) {
-        const size_t smem = (size_t)(TM_TQ * (d.heads * d.dk + 8) + TM_TK * (d.kv_heads * d.dk + 8) +
-                                     TM_TK * (d.kv_heads * d.dv + 8)) * 2 +
-                            (size_t)(d.heads * TM_TQ * TM_SS + d.heads * d.heads) * sizeof(float);
+        const bool pair = d.heads > 16;
+        const int hc = pair ? d.heads / 2 : d.heads, per = d.heads / d.kv_heads;
+        const int gc = pair ? (hc - 1) / per + 1 + ((hc % per) ? 1 : 0) : d.kv_heads;     // key/value heads a CTA stages at most
+        const int gcc = gc < d.kv_heads ? gc : d.kv_heads;
+        const size_t smem = (size_t)(TM_TQ * (hc * d.dk + 8) + TM_TK * (gcc * d.dk + 8) + TM_TK * (gcc * d.dv + 8)) * 2 +
+                            (size_t)(d.heads * TM_TQ * TM_SS + ((hc * d.heads + 3) & ~3)) * sizeof(float);
         if (smem <= 220 * 1024) {
-            dim3 grid((max_qlen + TM_TQ - 1) / TM_TQ, nseq);
+            const unsigned qtiles = (max_qlen + TM_TQ - 1) / TM_TQ;
+            dim3 grid(pair ? 2 * qtiles : qtiles, nseq);
             if (grid.y > 65535) return set_error("talk_attention: too many sequences");
-#define ASD_TM_CASE(N)                                                                                                \
+            cudaLaunchConfig_t lc = {};
+            lc.gridDim = grid, lc.blockDim = dim3(hc * 32), lc.dynamicSmemBytes = smem, lc.stream = stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = pair ? 2 : 1, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
+            lc.attrs = at, lc.numAttrs = 1;
+#define ASD_TM_CASE2(N, P)                                                                                            \
     {                                                                                                                 \
-        auto fn = talk_attention_mma_kernel<N>;                                                                       \
+        auto fn = talk_attention_mma_kernel<N, P>;                                                                    \
         static PerDeviceOnce once;                                                                                    \
         if (once.need()) ASD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
-        fn<<<grid, d.heads * 32, smem, stream>>>(ix, cu_q, seq_slot, q, ldq, d, talk, sink, cache, out, of32, ldo,     \
-                                                 out_scale);                                                          \
+        ASD_CUDA(cudaLaunchKernelEx(&lc, fn, ix, cu_q, seq_slot, q, ldq, d, talk, sink, cache, out, of32, ldo, out_scale)); \
     }
-            if (d.dv == 16) ASD_TM_CASE(2)
-            else if (d.dv == 32) ASD_TM_CASE(4)
-            else if (d.dv == 64) ASD_TM_CASE(8)
-            else ASD_TM_CASE(16)
+#define ASD_TM_CASE(N)                  \
+    if (pair) ASD_TM_CASE2(N, true)     \
+    else ASD_TM_CASE2(N, false)
+            if (d.dv == 16) {
+                ASD_TM_CASE(2)
+            } else if (d.dv == 32) {
+                ASD_TM_CASE(4)
+            } else if (d.dv == 64) {
+                ASD_TM_CASE(8)
+            } else {
+                ASD_TM_CASE(16)
+            }
 #undef ASD_TM_CASE
+#undef ASD_TM_CASE2
             count_launch(1);
             ASD_CUDA(cudaGetLastError());
             return 0;
@@ -715,14 +789,15 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
                     ASD_CUDA(cudaFuncSetAttribute(talk_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
                     ASD_CUDA(cudaFuncSetAttribute(talk_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
                 }
+                int* arrived = ws.ml && ws.rows >= ix.M ? reinterpret_cast<int*>(ws.ml) : nullptr;   // zeroed counters, one per token
                 if (cache.f32)
                     talk_decode_kernel<float><<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out, of32, ldo,
-                                                                                   out_scale, ws.o, nsplit);
+                                                                                   out_scale, ws.o, nsplit, arrived);
                 else
                     talk_decode_kernel<__nv_bfloat16><<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out,
-                                                                                           of32, ldo, out_scale, ws.o, nsplit);
+                                                                                           of32, ldo, out_scale, ws.o, nsplit, arrived);
                 count_launch(1);
-                if (nsplit > 1) {
+                if (nsplit > 1 && !arrived) {
                     const long long warps = (long long)ix.M * d.heads;
                     talk_merge_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(ws.o, nsplit, sink, out, of32, ldo, out_scale,
                                                                                      ix.M, d.heads, d.dv);

@@ -453,7 +453,8 @@ def test_both_window_attention_kernels_agree():
     Every value size the tensor-core kernel takes, one and several query heads per key/value head, windows shorter and
     longer than a key tile, prompts, portions that end inside a query tile and single tokens"""
     for heads, kv_heads, dim, vdim, size in ((4, 4, 32, 16, 100), (6, 2, 16, 32, 37), (8, 1, 64, 128, 130), (16, 4, 48, 64, 1000),
-                                             (3, 1, 80, 32, 7)):
+                                             (3, 1, 80, 32, 7), (32, 8, 32, 32, 90), (24, 3, 16, 64, 40), (18, 9, 16, 16, 500),
+                                             (20, 1, 48, 32, 33)):       # more than 16 heads: two CTAs share a query tile
         cfg = config([par(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, size=size, rot_dims=16, scale=0.3, softcap=15.0)])
         w = O.random_model(cfg, seed=55)
         w["l0.mix.left.sink"] = torch.linspace(-2.0, 4.0, heads).to(torch.bfloat16)
