@@ -557,7 +557,10 @@ __global__ void talk_merge_kernel(const float* part, int nsplit, const float* si
 // buffers, one barrier per tile); every warp mixes its head's row, updates the running softmax and adds the values with
 // each lane on four neighbouring value columns, the rows' addresses passed from lane to lane.  Small shared memory and
 // few registers: several CTAs share an SM and hide one another's loads.
-template <typename T>
+// DPL > 0 (key size = 8 DPL): eight lanes share a key row, DPL coordinates each, against query coordinates held in
+// registers, so that a row is read in whole 128-byte lines; four keys per step, sums closed by shuffles.  DPL = 0 (any
+// key size that is a multiple of the 16-byte piece): lane = key reads its own row.
+template <typename T, int DPL>
 __global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const float* q, long long ldq, TalkDims d,
                                                               const float* talk, const float* sink, PagedRows cache, void* out,
                                                               int of32, long long ldo, float out_scale, float* part, int nsplit,
@@ -596,13 +599,57 @@ __global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const
     const float* qh = qs + h * dk;
     const int groups = dv >> 2;            // four value columns per lane and group
     __syncthreads();
+    float qreg[DPL > 0 ? DPL : 1];
+    if constexpr (DPL > 0) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) qreg[i] = qh[(lane & 7) * DPL + i];
+    }
     int par = 0;
-    for (int kt = kt_lo; kt <= kt_hi; ++kt, par ^= 1) {
+    // a tile's row addresses are looked up one tile ahead, and lines that are needed later are asked for early: this
+    // tile's value rows before its key rows are read, the next tile's key rows behind them
+    auto row_of = [&](int kt) {
         const int j = kt * 32 + lane;
-        const bool ok = j >= lo_pos && j <= pos;
-        const long long row = ok ? cache_row(cache, slot, j) * row_elems : 0;
+        return kt <= kt_hi && j >= lo_pos && j <= pos ? cache_row(cache, slot, j) * row_elems : -1;
+    };
+    auto ask = [&](const T* p, int elems) {
+        for (int e = 0; e < elems; e += 128 / (int)sizeof(T)) asm volatile("prefetch.global.L1 [%0];" ::"l"(p + e));
+    };
+    long long row_next = row_of(kt_lo);
+    for (int kt = kt_lo; kt <= kt_hi; ++kt, par ^= 1) {
+        const bool ok = row_next >= 0;
+        const long long row = ok ? row_next : 0;
+        row_next = row_of(kt + 1);
         float s = 0.f;
-        if (ok) {
+        if (ok) ask(pool + row + nk + kvh * dv, dv);
+        if constexpr (DPL > 0) {
+            const int sub = lane & 7, kg = lane >> 3;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const long long rk = __shfl_sync(0xffffffffu, row, 4 * it + kg);      // a masked key reads row 0 of the pool
+                const uint4* kp = reinterpret_cast<const uint4*>(pool + rk + kvh * dk + sub * DPL);
+                uint4 r[DPL / VE];
+#pragma unroll
+                for (int u = 0; u < DPL / VE; ++u) r[u] = __ldg(kp + u);
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int u = 0; u < DPL / VE; ++u) {
+                    const T* x = reinterpret_cast<const T*>(&r[u]);
+#pragma unroll
+                    for (int i = 0; i < VE; i += 2) {
+                        s0 = fmaf(qreg[u * VE + i], (float)x[i], s0);
+                        s1 = fmaf(qreg[u * VE + i + 1], (float)x[i + 1], s1);
+                    }
+                }
+                float t = s0 + s1;
+                t += __shfl_xor_sync(0xffffffffu, t, 1);
+                t += __shfl_xor_sync(0xffffffffu, t, 2);
+                t += __shfl_xor_sync(0xffffffffu, t, 4);
+                const float mine = __shfl_sync(0xffffffffu, t, (lane & 3) * 8);     // key 4 it + (lane & 3)
+                if ((lane >> 2) == it) s = mine;
+            }
+            s *= d.scale;
+            if (d.softcap > 0.f) s = d.softcap * tanhf(s / d.softcap);
+        } else if (ok) {
             const uint4* kp = reinterpret_cast<const uint4*>(pool + row + kvh * dk);
             float s0 = 0.f, s1 = 0.f;
             for (int c0 = 0; c0 < dk; c0 += 8 * VE) {
@@ -624,6 +671,7 @@ __global__ void __launch_bounds__(1024, 1) talk_decode_kernel(SeqIndex ix, const
             s = (s0 + s1) * d.scale;
             if (d.softcap > 0.f) s = d.softcap * tanhf(s / d.softcap);
         }
+        if (row_next >= 0) ask(pool + row_next + kvh * dk, dk);
         float* sb = Ss + par * H * 32;
         sb[h * 32 + lane] = s;
         __syncthreads();
@@ -783,19 +831,28 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
             }
             const size_t smem = (size_t)(((d.heads * d.dk + 3) & ~3) + 3 * d.heads * 32 + d.heads * d.heads) * sizeof(float);
             dim3 grid(ix.M, nsplit);
-            if (smem <= 200 * 1024 && nsplit <= 65535) {
-                static PerDeviceOnce once;
-                if (once.need()) {
-                    ASD_CUDA(cudaFuncSetAttribute(talk_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-                    ASD_CUDA(cudaFuncSetAttribute(talk_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-                }
+            if (smem <= 48 * 1024 && nsplit <= 65535) {     // (the default limit of dynamic shared memory: no attribute to set)
                 int* arrived = ws.ml && ws.rows >= ix.M ? reinterpret_cast<int*>(ws.ml) : nullptr;   // zeroed counters, one per token
-                if (cache.f32)
-                    talk_decode_kernel<float><<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out, of32, ldo,
-                                                                                   out_scale, ws.o, nsplit, arrived);
-                else
-                    talk_decode_kernel<__nv_bfloat16><<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out,
-                                                                                           of32, ldo, out_scale, ws.o, nsplit, arrived);
+                const int dpl = (d.dk % 8 == 0 && (d.dk / 8) % ve == 0 && d.dk / 8 <= 32) ? d.dk / 8 : 0;
+#define ASD_TD_CASE(T_, D_)                                                                                            \
+    {                                                                                                                 \
+        auto fn = talk_decode_kernel<T_, D_>;                                                                         \
+        fn<<<grid, d.heads * 32, smem, stream>>>(ix, q, ldq, d, talk, sink, cache, out, of32, ldo, out_scale, ws.o,    \
+                                                 nsplit, arrived);                                                    \
+    }
+                if (cache.f32) {
+                    if (dpl == 4) ASD_TD_CASE(float, 4)
+                    else if (dpl == 8) ASD_TD_CASE(float, 8)
+                    else if (dpl == 16) ASD_TD_CASE(float, 16)
+                    else if (dpl == 32) ASD_TD_CASE(float, 32)
+                    else ASD_TD_CASE(float, 0)
+                } else {
+                    if (dpl == 8) ASD_TD_CASE(__nv_bfloat16, 8)
+                    else if (dpl == 16) ASD_TD_CASE(__nv_bfloat16, 16)
+                    else if (dpl == 32) ASD_TD_CASE(__nv_bfloat16, 32)
+                    else ASD_TD_CASE(__nv_bfloat16, 0)
+                }
+#undef ASD_TD_CASE
                 count_launch(1);
                 if (nsplit > 1 && !arrived) {
                     const long long warps = (long long)ix.M * d.heads;
