@@ -41,10 +41,13 @@ __global__ void __launch_bounds__(LC_CH) lowrank_channels_kernel(const float* a,
     const int n = p.n;
     const int c0 = blockIdx.x * LC_CH, m0 = blockIdx.y * LC_TOK;
     const int nt = min(LC_TOK, M - m0);
+    // unrolled: eight independent loads in flight per thread instead of a load-then-store chain
+#pragma unroll 8
     for (int i = threadIdx.x; i < LC_CH * p.low; i += LC_CH) {
         const int c = i / p.low, r = i - c * p.low;
         wT[r * LC_CH + c] = c0 + c < n ? __ldg(p.w2 + (long long)(c0 + c) * p.low + r) : 0.f;
     }
+#pragma unroll 4
     for (int i = threadIdx.x; i < LC_TOK * p.low; i += LC_CH) {
         const int t = i / p.low, r = i - t * p.low;
         float v = t < nt ? __ldg(a + (long long)(m0 + t) * lda + r) : 0.f;
@@ -94,18 +97,25 @@ __global__ void short_conv_kernel(SeqIndex ix, const float* in, long long ld, co
     while (above < n - 1 && m - above - 1 >= 0 && ix.token_slot[m - above - 1] == slot &&
            ix.positions[m - above - 1] == pos - above - 1)
         ++above;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;       // a channel per thread
-    if (c >= C) return;
-    float acc = 0.f;
+    // four channels per thread, blockDim apart, their loads independent of one another
+    const int cb = blockIdx.y * blockDim.x * 4 + threadIdx.x;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < n; ++j) {
         const int back = n - 1 - j;       // taps' last column weighs the current position
         const int p = pos - back;
         if (p < 0) continue;
-        const float v = back <= above ? __ldg(in + (long long)(m - back) * ld + c)
-                                      : __ldg(ring + ((long long)slot * ring_n + p % ring_n) * C + c);
-        acc = fmaf(__ldg(taps + (long long)c * n + j), v, acc);
+        const float* src = back <= above ? in + (long long)(m - back) * ld : ring + ((long long)slot * ring_n + p % ring_n) * C;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = cb + u * blockDim.x;
+            if (c < C) acc[u] = fmaf(__ldg(taps + (long long)c * n + j), __ldg(src + c), acc[u]);
+        }
     }
-    out[(long long)m * C + c] = acc / (1.f + expf(-acc));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int c = cb + u * blockDim.x;
+        if (c < C) out[(long long)m * C + c] = acc[u] / (1.f + expf(-acc[u]));
+    }
 }
 
 // the last ring_n new positions of every sequence leave their inputs behind (runs after short_conv_kernel has read)
@@ -116,7 +126,8 @@ __global__ void conv_commit_kernel(SeqIndex ix, const int* cu_q, const float* in
     for (int m = t0 + blockIdx.y; m < t1; m += gridDim.y) {
         const int pos = ix.positions[m], slot = ix.token_slot[m];
         float* dst = ring + ((long long)slot * ring_n + pos % ring_n) * C;
-        for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = in[(long long)m * ld + c];
+#pragma unroll 8
+        for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = __ldg(in + (long long)m * ld + c);
     }
 }
 
@@ -499,7 +510,7 @@ int launch_short_conv(const SeqIndex& ix, const float* in, long long ld, const f
     if (n_taps <= 0 || (n_taps > 1 && (!ring || ring_n < n_taps - 1)))
         return set_error("short_conv: %d taps need a ring of at least %d carried inputs", n_taps, n_taps - 1);
     const int threads = C >= 1024 ? 256 : 128;
-    dim3 grid(ix.M, (C + threads - 1) / threads);
+    dim3 grid(ix.M, (C + 4 * threads - 1) / (4 * threads));
     if (grid.y > 65535) return set_error("short_conv: too many channels");
     short_conv_kernel<<<grid, threads, 0, stream>>>(ix, in, ld, taps, n_taps, C, ring, ring_n > 0 ? ring_n : 1, out);
     count_launch(1);

@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(128) moe_logits_kernel(const void* x, int xf32
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 4
         for (int d = threadIdx.x; d < D; d += 128) {
             const float xv = ldx(x, (long long)m * D + d, xf32);
 #pragma unroll

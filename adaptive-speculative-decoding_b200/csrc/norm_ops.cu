@@ -47,6 +47,7 @@ __global__ void row_close_kernel(RowClose c) {
         }
         post = 1.f / sqrtf(block_sum(ss, red) / (float)D + c.eps);
     }
+#pragma unroll 4
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float v = c.x_in ? c.x_in[in_base + d] : 0.f;
         if (c.y) v += c.post_w ? c.y[base + d] * post * (off + c.post_w[d]) : c.y[base + d];
