@@ -268,7 +268,7 @@ int launch_short_conv(const SeqIndex& ix, const float* in, long long ld, const f
                       const float* ring, int ring_n, float* out, cudaStream_t stream);
 int launch_conv_commit(const SeqIndex& ix, const int* cu_q, int nseq, const float* in, long long ld, int C, float* ring,
                        int ring_n, cudaStream_t stream);
-// The vectors a position's recurrence step reads, rv fp32 [M][heads][4 or 5][dk] and sc fp32 [M][heads][4] (layout in
+// The vectors a position's recurrence step reads, rv fp32 [M][heads][3 or 5][dk] and sc fp32 [M][heads][4] (layout in
 // delta_rule.cu).  Gated rule (general = 0): q, k = fp32 rows ld apart holding kv_heads * dk values (head h reads key
 // head h / (heads / kv_heads)), made unit vectors (x / sqrt(sum x^2 + tiny)), q times q_scale; beta = raw rows (ld_beta
 // apart, one per head) that pass a sigmoid; decay fp32 [M][heads * dk].  Generalised rule (general = 1): q = the

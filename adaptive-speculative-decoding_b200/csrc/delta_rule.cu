@@ -5,13 +5,13 @@
 // and the row kernels around them: channel functions of a low-rank projection (decays, gates), the short causal
 // convolution with its carried inputs, the preparation of a position's vectors, the per-head norm and gate of the result.
 //
-// Both rules are one kernel.  A position's step reads the state it starts from through two dot products per value column,
-//   A = sum_r S[r] x1[r],  B = sum_r S[r] x2[r],
-// and then updates S[r] <- d[r] S[r] + y[r] cA + k[r] cB with cA = -sa A, cB = sb v, while o = B + cA s1 + cB s2:
-//   gated:        d = g, x1 = g * k, x2 = g * q, y = k, sa = sb = beta, s1 = s2 = k . q
-//   generalised:  d = w, x1 = n, x2 = w * r, y = a * n, sa = sb = 1, s1 = (a * n) . r, s2 = k . r
-// (the read-out of the updated state is expanded, so that one pass over the old state serves the correction and the
-// result).  delta_prep_kernel forms these vectors; delta_recurrence_kernel holds a CTA's 32 value columns of the state
+// Both rules are one kernel with one exchange per position.  Generalised rule: a step reads the state it starts from
+// through two dot products per value column, A = sum_r S[r] n[r] and B = sum_r S[r] (w * r)[r], and then updates
+// S[r] <- w[r] S[r] - (a * n)[r] A + k[r] v, while o = B - A s1 + v s2 with s1 = (a * n) . r, s2 = k . r (the read-out
+// of the updated state is expanded, so that one pass over the old state serves the correction and the result); five
+// vectors per position (w, n, w * r, k, a * n).  Gated rule, in the order it is written: S[r] <- g[r] S[r], then
+// A = sum_r S[r] k[r] and B = sum_r S[r] q[r] in the same pass, u = beta (v - A), S[r] <- S[r] + k[r] u (k still in
+// registers: nothing is read after the exchange), o = B + u (k . q); three vectors per position (g, k, q).  delta_prep_kernel forms these vectors; delta_recurrence_kernel holds a CTA's 32 value columns of the state
 // in registers, the key rows cut into slices over its warps, for the whole run of new positions.  The arithmetic per
 // position is the same whatever the chunking or the batch.  State: fp32 [slot][ring][head][dk][dv], entry p % ring =
 // the state after position p.
@@ -132,13 +132,14 @@ __global__ void conv_commit_kernel(SeqIndex ix, const int* cu_q, const float* in
 }
 
 // ------------------------------------------------------------------------------------------ a position's vectors
-// one warp per (token, head): rv[m][h][vec][dk] with vec = d, x1, x2, k (, y) and sc[m][h][4] = sa, sb, s1, s2
+// one warp per (token, head): rv[m][h][vec][dk] with vec = g, k, q (gated) or w, n, w * r, k, a * n (generalised) and
+// sc[m][h][4] = beta, -, k . q, - (gated) or -, -, (a * n) . r, k . r (generalised)
 __global__ void delta_prep_kernel(DeltaPrep p, int M) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (idx >= (long long)M * p.heads) return;
     const int m = (int)(idx / p.heads), h = (int)(idx - (long long)m * p.heads);
-    const int dk = p.dk, nv = p.general ? 5 : 4;
+    const int dk = p.dk, nv = p.general ? 5 : 3;
     const int kvh = h / (p.heads / p.kv_heads);
     const float* q = p.q + (long long)m * p.ld + (long long)kvh * dk;
     const float* k = p.k + (long long)m * p.ld + (long long)kvh * dk;
@@ -158,9 +159,8 @@ __global__ void delta_prep_kernel(DeltaPrep p, int M) {
         for (int i = lane; i < dk; i += 32) {
             const float kv = k[i] * kn, qv = q[i] * qn, dv = d[i];
             rv[i] = dv;
-            rv[dk + i] = dv * kv;
-            rv[2 * dk + i] = dv * qv;
-            rv[3 * dk + i] = kv;
+            rv[dk + i] = kv;
+            rv[2 * dk + i] = qv;
             s1 = fmaf(kv, qv, s1);
         }
         s1 = warp_sum(s1);
@@ -204,7 +204,7 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 }
 
 // ROWS state rows per thread; warps = slices of ROWS key rows (rows beyond dk are staged as zeros and keep a zero
-// state).  NV = 4: y is k (gated); NV = 5: y has its own vector (generalised).  CH positions are staged per chunk by
+// state).  NV = 3: the gated rule; NV = 5: the generalised rule.  CH positions are staged per chunk by
 // cp.async, one chunk ahead of the arithmetic.
 template <int ROWS, int NV, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, const int* cu_q, const int* seq_slot,
@@ -286,10 +286,44 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
         for (int t = 0; t < nt; ++t, par ^= 1) {
             const float* vt = vec + t * NV * dkp + r0;
             const float4* d4 = reinterpret_cast<const float4*>(vt);
+            float* rp = red + (size_t)par * RS * 64;
+            float o_t;
+            if constexpr (NV == 3) {
+                const float4* k4 = reinterpret_cast<const float4*>(vt + dkp);
+                const float4* q4 = reinterpret_cast<const float4*>(vt + 2 * dkp);
+                float kr[ROWS];
+                float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+                for (int r = 0; r < ROWS; r += 4) {
+                    const float4 dd = d4[r >> 2], kk = k4[r >> 2], qq = q4[r >> 2];
+                    kr[r] = kk.x, kr[r + 1] = kk.y, kr[r + 2] = kk.z, kr[r + 3] = kk.w;
+                    S[r] *= dd.x, S[r + 1] *= dd.y, S[r + 2] *= dd.z, S[r + 3] *= dd.w;
+                    a0 = fmaf(S[r], kk.x, a0);
+                    a1 = fmaf(S[r + 1], kk.y, a1);
+                    a0 = fmaf(S[r + 2], kk.z, a0);
+                    a1 = fmaf(S[r + 3], kk.w, a1);
+                    b0 = fmaf(S[r], qq.x, b0);
+                    b1 = fmaf(S[r + 1], qq.y, b1);
+                    b0 = fmaf(S[r + 2], qq.z, b0);
+                    b1 = fmaf(S[r + 3], qq.w, b1);
+                }
+                rp[warp * 64 + lane] = a0 + a1;
+                rp[warp * 64 + 32 + lane] = b0 + b1;
+                __syncthreads();
+                float A = 0.f, B = 0.f;
+                for (int w = 0; w < RS; ++w) {      // every warp adds the slices in index order: the same totals everywhere
+                    A += rp[w * 64 + lane];
+                    B += rp[w * 64 + 32 + lane];
+                }
+                const float u = ss[t * 4 + 0] * (vs[t * 32 + lane] - A);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) S[r] = fmaf(kr[r], u, S[r]);
+                o_t = fmaf(u, ss[t * 4 + 2], B);
+            } else {
             const float4* x14 = reinterpret_cast<const float4*>(vt + dkp);
             const float4* x24 = reinterpret_cast<const float4*>(vt + 2 * dkp);
             const float4* k4 = reinterpret_cast<const float4*>(vt + 3 * dkp);
-            const float4* y4 = reinterpret_cast<const float4*>(vt + (NV == 5 ? 4 : 3) * dkp);
+            const float4* y4 = reinterpret_cast<const float4*>(vt + 4 * dkp);
             float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
             for (int r = 0; r < ROWS; r += 4) {
@@ -303,7 +337,6 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
                 b0 = fmaf(S[r + 2], z.z, b0);
                 b1 = fmaf(S[r + 3], z.w, b1);
             }
-            float* rp = red + (size_t)par * RS * 64;
             rp[warp * 64 + lane] = a0 + a1;
             rp[warp * 64 + 32 + lane] = b0 + b1;
             __syncthreads();
@@ -313,7 +346,7 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
                 B += rp[w * 64 + 32 + lane];
             }
             const float vv = vs[t * 32 + lane];
-            const float cA = -ss[t * 4 + 0] * A, cB = ss[t * 4 + 1] * vv;
+            const float cA = -A, cB = vv;
 #pragma unroll
             for (int r = 0; r < ROWS; r += 4) {
                 const float4 dd = d4[r >> 2], kk = k4[r >> 2], yy = y4[r >> 2];
@@ -322,9 +355,10 @@ __global__ void __launch_bounds__(MAXT, 1) delta_recurrence_kernel(SeqIndex ix, 
                 S[r + 2] = fmaf(kk.z, cB, fmaf(yy.z, cA, dd.z * S[r + 2]));
                 S[r + 3] = fmaf(kk.w, cB, fmaf(yy.w, cA, dd.w * S[r + 3]));
             }
+            o_t = fmaf(cB, ss[t * 4 + 3], fmaf(cA, ss[t * 4 + 2], B));
+            }
             const int m = c0 + t;
-            if (warp == 0 && col_ok)
-                out[(long long)m * heads * dv + hv + col] = fmaf(cB, ss[t * 4 + 3], fmaf(cA, ss[t * 4 + 2], B));
+            if (warp == 0 && col_ok) out[(long long)m * heads * dv + hv + col] = o_t;
             if (t1 - m <= ring && col_ok) {     // the last `ring` new positions leave their state behind
                 float* dst = st_slot + (long long)((p0 + (m - t0)) % ring) * st_entry + st_head;
 #pragma unroll
@@ -418,10 +452,41 @@ __global__ void __launch_bounds__(512, 1) delta_recurrence_cols_kernel(SeqIndex 
         const float* ss = vs + CH * dvp;
         for (int t = 0; t < nt; ++t) {
             const float4* d4 = reinterpret_cast<const float4*>(vec + t * NV * DKP + part * PS);
+            float o_t;
+            if constexpr (NV == 3) {
+                const float4* k4 = d4 + DKP / 4;
+                const float4* q4 = d4 + 2 * (DKP / 4);
+                float kr[ROWS];
+                float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+                for (int r = 0; r < ROWS; r += 4) {
+                    const float4 dd = d4[r >> 2], kk = k4[r >> 2], qq = q4[r >> 2];
+                    kr[r] = kk.x, kr[r + 1] = kk.y, kr[r + 2] = kk.z, kr[r + 3] = kk.w;
+                    S[r] *= dd.x, S[r + 1] *= dd.y, S[r + 2] *= dd.z, S[r + 3] *= dd.w;
+                    a0 = fmaf(S[r], kk.x, a0);
+                    a1 = fmaf(S[r + 1], kk.y, a1);
+                    a0 = fmaf(S[r + 2], kk.z, a0);
+                    a1 = fmaf(S[r + 3], kk.w, a1);
+                    b0 = fmaf(S[r], qq.x, b0);
+                    b1 = fmaf(S[r + 1], qq.y, b1);
+                    b0 = fmaf(S[r + 2], qq.z, b0);
+                    b1 = fmaf(S[r + 3], qq.w, b1);
+                }
+                float A = a0 + a1, B = b0 + b1;
+#pragma unroll
+                for (int o = 1; o < PARTS; o <<= 1) {
+                    A += __shfl_xor_sync(0xffffffffu, A, o);
+                    B += __shfl_xor_sync(0xffffffffu, B, o);
+                }
+                const float u = ss[t * 4 + 0] * (vs[t * dvp + col] - A);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) S[r] = fmaf(kr[r], u, S[r]);
+                o_t = fmaf(u, ss[t * 4 + 2], B);
+            } else {
             const float4* x14 = d4 + DKP / 4;
             const float4* x24 = d4 + 2 * (DKP / 4);
             const float4* k4 = d4 + 3 * (DKP / 4);
-            const float4* y4 = d4 + (NV == 5 ? 4 : 3) * (DKP / 4);
+            const float4* y4 = d4 + 4 * (DKP / 4);
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
 #pragma unroll
             for (int r = 0; r < ROWS; r += 4) {
@@ -442,7 +507,7 @@ __global__ void __launch_bounds__(512, 1) delta_recurrence_cols_kernel(SeqIndex 
                 B += __shfl_xor_sync(0xffffffffu, B, o);
             }
             const float vv = vs[t * dvp + col];
-            const float cA = -ss[t * 4 + 0] * A, cB = ss[t * 4 + 1] * vv;
+            const float cA = -A, cB = vv;
 #pragma unroll
             for (int r = 0; r < ROWS; r += 4) {
                 const float4 dd = d4[r >> 2], kk = k4[r >> 2], yy = y4[r >> 2];
@@ -451,8 +516,10 @@ __global__ void __launch_bounds__(512, 1) delta_recurrence_cols_kernel(SeqIndex 
                 S[r + 2] = fmaf(kk.z, cB, fmaf(yy.z, cA, dd.z * S[r + 2]));
                 S[r + 3] = fmaf(kk.w, cB, fmaf(yy.w, cA, dd.w * S[r + 3]));
             }
+            o_t = fmaf(cB, ss[t * 4 + 3], fmaf(cA, ss[t * 4 + 2], B));
+            }
             const int m = c0 + t;
-            if (col_ok && part == 0) out[(long long)m * heads * dv + hv + col] = fmaf(cB, ss[t * 4 + 3], fmaf(cA, ss[t * 4 + 2], B));
+            if (col_ok && part == 0) out[(long long)m * heads * dv + hv + col] = o_t;
             if (t1 - m <= ring && col_ok) {     // the last `ring` new positions leave their state behind
                 float* dst = st_slot + (long long)((p0 + (m - t0)) % ring) * st_entry + st_head;
 #pragma unroll
@@ -550,7 +617,7 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     // steps of single tokens: the state is read and written once per position and the shuffle form keeps more loads in
     // flight; prompts and portions: the slices over warps read every staged vector once per warp as a broadcast
     if (ix.M <= 2 * nseq && dk <= 128 && ((dv + 32 / parts - 1) / (32 / parts)) * 32 <= 512) {   // row blocks closed by shuffles: no barrier per position
-        const int nvv = general ? 5 : 4, dkp = 36 * parts;
+        const int nvv = general ? 5 : 3, dkp = 36 * parts;
         const int cpw = 32 / parts, warps = (dv + cpw - 1) / cpw, dvp = warps * cpw;
         int ch = 16;
         auto need = [&](int c) { return (size_t)(2 * (c * nvv * dkp + c * dvp + c * 4)) * sizeof(float); };
@@ -572,7 +639,7 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
         if (general) {
             ASD_DC_PARTS(5)
         } else {
-            ASD_DC_PARTS(4)
+            ASD_DC_PARTS(3)
         }
 #undef ASD_DC_PARTS
 #undef ASD_DC_CASE
@@ -583,7 +650,7 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     int rows = 4;
     while (rows < 32 && rows * 4 < dk) rows *= 2;     // four warps up to key size 128, then more
     const int RS = (dk + rows - 1) / rows;
-    const int dkp = RS * rows, nv = general ? 5 : 4;
+    const int dkp = RS * rows, nv = general ? 5 : 3;
     int ch = 16;   // positions per staged chunk: as many as two buffers of a head's vectors leave room for
     auto need = [&](int c) { return (size_t)(2 * (c * nv * dkp + c * 36) + 2 * RS * 64) * sizeof(float); };
     while (ch > 1 && need(ch) > 200 * 1024) ch >>= 1;
@@ -607,7 +674,7 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     if (general) {
         ASD_DR_ROWS(5)
     } else {
-        ASD_DR_ROWS(4)
+        ASD_DR_ROWS(3)
     }
 #undef ASD_DR_ROWS
 #undef ASD_DR_CASE
