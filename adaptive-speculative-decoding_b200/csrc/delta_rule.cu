@@ -619,7 +619,8 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     if (ix.M <= 2 * nseq && dk <= 128 && ((dv + 32 / parts - 1) / (32 / parts)) * 32 <= 512) {   // row blocks closed by shuffles: no barrier per position
         const int nvv = general ? 5 : 3, dkp = 36 * parts;
         const int cpw = 32 / parts, warps = (dv + cpw - 1) / cpw, dvp = warps * cpw;
-        int ch = 16;
+        int ch = 16;   // positions per staged chunk; steps of few tokens per sequence stage (and clear) no more than they use
+        while (ch > 1 && (long long)(ch / 2) * nseq >= ix.M) ch >>= 1;
         auto need = [&](int c) { return (size_t)(2 * (c * nvv * dkp + c * dvp + c * 4)) * sizeof(float); };
         while (ch > 1 && need(ch) > 100 * 1024) ch >>= 1;
         dim3 grid(nseq, heads);
@@ -652,6 +653,7 @@ int launch_delta_recurrence(const SeqIndex& ix, const int* cu_q, const int* seq_
     const int RS = (dk + rows - 1) / rows;
     const int dkp = RS * rows, nv = general ? 5 : 3;
     int ch = 16;   // positions per staged chunk: as many as two buffers of a head's vectors leave room for
+    while (ch > 1 && (long long)(ch / 2) * nseq >= ix.M) ch >>= 1;
     auto need = [&](int c) { return (size_t)(2 * (c * nv * dkp + c * 36) + 2 * RS * 64) * sizeof(float); };
     while (ch > 1 && need(ch) > 200 * 1024) ch >>= 1;
     const size_t smem = need(ch);
