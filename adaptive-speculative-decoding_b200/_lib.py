@@ -72,6 +72,22 @@ class MavipelConfigC(ctypes.Structure):
                 ("ring", ctypes.c_int), ("dtype", ctypes.c_int)]
 
 
+class LukopelLayerC(ctypes.Structure):
+    """mirror of ``asd_lukopel_layer_config``"""
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "heads", "kv_heads", "dim", "vdim", "norm_whole", "v_unit", "gated", "chunk", "far", "temp_every", "ff_kind",
+        "ff")] + [(n, ctypes.c_float) for n in ("scale", "temp_coef")]
+
+
+class LukopelConfigC(ctypes.Structure):
+    """mirror of ``asd_lukopel_config``"""
+    _fields_ = [("width", ctypes.c_int), ("vocab", ctypes.c_int), ("n_layers", ctypes.c_int), ("eps", ctypes.c_float),
+                ("embed_scale", ctypes.c_float), ("streams", ctypes.c_int), ("max_positions", ctypes.c_int),
+                ("loop_start", ctypes.c_int), ("loop_stop", ctypes.c_int), ("loop_times", ctypes.c_int),
+                ("max_tokens", ctypes.c_int), ("page_size", ctypes.c_int), ("ring", ctypes.c_int),
+                ("dtype", ctypes.c_int)]
+
+
 def library_path() -> str:
     return os.path.join(_HERE, "libasd_b200.so")
 
@@ -155,6 +171,16 @@ def lib() -> ctypes.CDLL:
         "asd_mavipel_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
         "asd_mavipel_profile_read": (i32, [vp, vp, vp, i32]),
         "asd_mavipel_device_error": (i32, [vp]),
+        "asd_lukopel_create": (vp, [vp, vp]),
+        "asd_lukopel_destroy": (None, [vp]),
+        "asd_lukopel_set_tensor": (i32, [vp, i32, c.c_char_p, vp]),
+        "asd_lukopel_cache_bytes": (sz, [vp, i32]),
+        "asd_lukopel_state_bytes": (sz, [vp, i32]),
+        "asd_lukopel_set_cache": (i32, [vp, vp, i32, vp, i32, i32, vp]),
+        "asd_lukopel_set_option": (i32, [vp, c.c_char_p, i32]),
+        "asd_lukopel_forward": (i32, [vp, vp, vp, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp, c.c_longlong, vp, vp]),
+        "asd_lukopel_profile_read": (i32, [vp, vp, vp, i32]),
+        "asd_lukopel_device_error": (i32, [vp]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(L, name, None)

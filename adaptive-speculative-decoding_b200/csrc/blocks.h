@@ -188,7 +188,9 @@ int launch_embed_normed(const SeqIndex& ix, const void* embed, int wf32, const f
                         int D, cudaStream_t stream);
 // Feed-forward activations over `rows` rows: out[r][f] = gelu_tanh(z[r][f]) with z rows of F floats, or (gated)
 // silu(z[r][f]) * z[r][F + f] with z rows of 2 F floats (gate half, then up half); out in the engine's element type
-int launch_ff_act(const float* z, void* out, int of32, long long rows, int F, int gated, cudaStream_t stream);
+// mode 2: relu(z[r][f] + bias[f])^2.  bias (optional, fp32 [F]; mode 1: [2 F]) is added to z first in every mode.
+int launch_ff_act(const float* z, void* out, int of32, long long rows, int F, int gated, cudaStream_t stream,
+                  const float* bias = nullptr);
 // out[m][0 .. n) = in[m][0 .. n) / rms * w (plain weight; plus_one: 1 + w), rows ld_in / ld_out apart
 int launch_rms_rows(const float* in, long long ld_in, const float* w, int plus_one, float eps, void* out, int of32,
                     long long ld_out, int M, int n, cudaStream_t stream);
@@ -330,6 +332,79 @@ int launch_talk_attention(const SeqIndex& ix, const int* cu_q, const int* seq_sl
                           const float* q, long long ldq, const TalkDims& d, const float* talk, const float* sink,
                           const PagedRows& cache, void* out, int of32, long long ldo, float out_scale, const AttnSplit& ws,
                           cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- residual_streams.cu
+// Several residual streams per token (hyper-connections): xs fp32 [M][S][D].  A sublayer reads u = sum_s read[s] x_s and
+// its result y goes back as x_t <- sum_s mix[s][t] x_s + write[t] * y for all t at once.
+// xs[m][s] = embed[token] * scale + pos_table[position] for every s (pos_table optional, engine's element type)
+int launch_embed_streams(const SeqIndex& ix, const void* embed, const void* pos_table, int wf32, float scale, float* xs,
+                         int S, int D, cudaStream_t stream);
+// One pass over a row: (1) if y: the streams take the sublayer's result (y_bias, optional [D], is added to y first);
+// (2) if read: u = sum_s read[s] x_s over the new streams; u_out (optional, fp32 [M][D]) receives it, and with next_w
+// hn = u / rms(u) * next_w in the engine's element type.  With `rows`, row r reads xs[rows[r]] (no write-back then).
+struct StreamClose {
+    float* xs = nullptr;            // [M][S][D]
+    const int* rows = nullptr;
+    const float* y = nullptr;       // [M][D]
+    const float* y_bias = nullptr;  // [D]
+    const float* mix = nullptr;     // [S][S], from-stream major
+    const float* write = nullptr;   // [S]
+    const float* read = nullptr;    // [S] (nullptr with want_sum: all ones)
+    int want_sum = 0;
+    float* u_out = nullptr;
+    const float* next_w = nullptr;  // [D]
+    void* hn = nullptr;
+    int hn_f32 = 0;
+    float eps = 0.f;
+    int M = 0, S = 1, D = 0;
+};
+int launch_stream_close(const StreamClose& c, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------- mixed_attention.cu
+// Grouped-query softmax attention whose softmax WEIGHTS may be mixed across the heads (w'_h = sum_g talk[h][g] w_g),
+// with a learned bias per (distance, head) on the scores, a causal mask that may be cut into chunks counted from
+// position 0, and a gate per head on the result.  Cache row per position: [kv_heads * dk keys | kv_heads * dv values].
+struct MixDims {
+    int heads, kv_heads, dk, dv;
+    int chunk;          // 0: position i sees every j <= i; else only those with j / chunk == i / chunk
+    float scale;
+};
+// What the projections pass before the attention.  qkv fp32 rows (ld floats apart) = [heads * dk | kv_heads * dk |
+// kv_heads * dv].  Adds the biases (same layout, optional); RMS-norms queries and keys either head by head (weights [dk],
+// norm_whole = 0) or over the whole projection (weights [heads * dk] and [kv_heads * dk], norm_whole = 1); multiplies the
+// queries by 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1) (temp_every 0: not) and by head_factor[head]
+// (optional); divides every value head by its root mean square (v_unit); leaves the queries in place and appends keys
+// and values to the cache.
+struct MixPost {
+    const float* bias = nullptr;
+    const float* q_norm = nullptr;
+    const float* k_norm = nullptr;
+    int norm_whole = 0;
+    float temp_coef = 0.f;
+    int temp_every = 0;
+    const float* head_factor = nullptr;
+    int v_unit = 0;
+    float eps = 0.f;
+};
+int launch_mix_post(const SeqIndex& ix, float* qkv, long long ld, const MixDims& d, const MixPost& p,
+                    const PagedRows& cache, cudaStream_t stream);
+// 0 if the kernels take these sizes (dv <= 128, dk <= 512, at most 64 heads when the weights are mixed), else -1 and
+// the error text
+int mix_attention_check(const MixDims& d, int talk);
+// Workspace: stats fp32 [2][shares][M][heads] (maximum and sum of every key share), part fp32 [shares][M][heads * dv].
+struct MixWork {
+    float* stats = nullptr;
+    float* part = nullptr;
+    long long stats_elems = 0, part_elems = 0;
+};
+// out[m][h][:] (rows ldo apart, engine's element type) = sigmoid(gate[m][h]) * sum_j w'_h[j] v[j].  dist_bias fp32
+// [far + 1][heads]: the bias at distance min(i - j, far) (nullptr: none); talk fp32 [heads][heads] (nullptr: no mixing);
+// gate fp32 rows ldg apart, one raw value per head (nullptr: none).  Steps of few tokens cut the keys into shares for
+// several CTAs.
+int launch_mix_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+                         const float* q, long long ldq, const MixDims& d, const float* dist_bias, int far,
+                         const float* talk, const float* gate, long long ldg, const PagedRows& cache, void* out, int of32,
+                         long long ldo, const MixWork& ws, cudaStream_t stream);
 
 int preload_blocks();
 

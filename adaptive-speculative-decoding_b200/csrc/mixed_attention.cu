@@ -1,0 +1,545 @@
+// Grouped-query softmax attention whose softmax weights are mixed across the heads AFTER the softmax,
+//   w_g[i][j] = softmax_j( scale * q_g[i] . k[j] + bias[min(i - j, far)][g] ),   w'_h = sum_g talk[h][g] w_g,
+//   o_h[i] = sigmoid(gate[i][h]) * sum_j w'_h[i][j] v[j],
+// over a causal mask that may be cut into chunks counted from position 0.  Mixing normalised weights needs every head's
+// softmax denominator before any value is read, so the work is two passes over the keys:
+//   stats  one CTA per (query tile, key/value group, key share): maximum and sum of exponentials of every (query, head);
+//   apply  one CTA per (query tile, key share): recomputes the scores of ALL heads for a key tile, turns them into
+//          normalised weights, mixes them across the heads in shared memory and multiplies with the values.
+// Because the weights are normalised with the final statistics, the key shares' partial results simply add (merge kernel,
+// fixed order).  Scores, weights and sums are fp32; keys and values come from the paged cache in its element type.
+// Without mixing (talk == nullptr) the same two passes run with one key/value group per CTA.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "asd_internal.h"
+#include "blocks.h"
+#include "elem.cuh"
+
+namespace asd {
+
+namespace {
+
+constexpr int KT = 64;          // keys per tile
+constexpr int PS = KT + 16;     // floats between the weight rows of a tile (two rows of a warp fall into different banks)
+constexpr int NT = 256;         // threads: 16 row lanes (ty) x 16 key / column lanes (tx)
+constexpr int MAX_ROWS = 128;   // (head, query) pairs of a CTA
+constexpr int SLOTS = 8;        // result rows a thread accumulates (over all of the CTA's key/value groups)
+
+struct MixArgs {
+    SeqIndex ix;
+    const int* cu_q;
+    const int* seq_slot;
+    const float* q;
+    long long ldq;
+    MixDims d;
+    const float* dist_bias;
+    int far;
+    const float* talk;
+    const float* gate;
+    long long ldg;
+    PagedRows cache;
+    void* out;
+    int of32;
+    long long ldo;
+    float* stats;
+    float* part;
+    int QT, shares, gp, rag, dkp, dvp, vec;
+};
+
+struct Layout {
+    int q, kv, p, w, talk, m, l, off, total;   // float offsets
+};
+__host__ __device__ inline Layout mix_layout(int rows, int dkp, int dvp, int heads, bool apply, bool talk) {
+    Layout L;
+    int o = 0;
+    L.q = o, o += rows * dkp;
+    const int kvw = (dkp + 4) > dvp ? (dkp + 4) : dvp;
+    L.kv = o, o += KT * kvw;
+    L.p = o, o += apply ? rows * PS : 0;
+    L.w = o, o += (apply && talk) ? rows * PS : 0;
+    L.talk = o, o += (apply && talk) ? heads * heads : 0;
+    L.m = o, o += apply ? rows : 0;
+    L.l = o, o += apply ? rows : 0;
+    o = (o + 1) & ~1;
+    L.off = o, o += 2 * KT;   // KT 64-bit row offsets
+    L.total = o;
+    return L;
+}
+
+// cache rows [kb, kb + nk) of one key/value head -> dst[key][np] fp32 (zeros beyond n and beyond nk)
+template <typename T>
+__device__ __forceinline__ void load_tile(const T* pool, const long long* rowoff, int nk, int head_off, int n, int np,
+                                          int stride, float* dst, int vec) {
+    const int n4 = np >> 2;
+    for (int idx = threadIdx.x; idx < KT * n4; idx += NT) {
+        const int key = idx / n4, d = (idx - key * n4) << 2;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (key < nk) {
+            const T* src = pool + rowoff[key] + head_off + d;
+            if (vec) {
+                if constexpr (sizeof(T) == 2) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+                    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                    v = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+                } else {
+                    v = *reinterpret_cast<const float4*>(src);
+                }
+            } else {
+                if (d + 0 < n) v.x = ldf(src + 0);
+                if (d + 1 < n) v.y = ldf(src + 1);
+                if (d + 2 < n) v.z = ldf(src + 2);
+                if (d + 3 < n) v.w = ldf(src + 3);
+            }
+        }
+        *reinterpret_cast<float4*>(dst + (size_t)key * stride + d) = v;
+    }
+}
+
+template <typename T, bool APPLY, int CB>
+__global__ void __launch_bounds__(NT) mix_attn_kernel(MixArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, QT = a.QT, chunk = a.d.chunk;
+    const int b = blockIdx.y;
+    const int seq_end = a.cu_q[b + 1];
+    const int q_beg = a.cu_q[b] + blockIdx.x * QT;
+    if (q_beg >= seq_end) return;
+    const int nq = min(QT, seq_end - q_beg);
+    const int share = blockIdx.z % a.shares, gsel = blockIdx.z / a.shares;
+    int gc0, gc1, hbeg, hend;
+    if (!APPLY) {
+        gc0 = gsel, gc1 = gsel + 1, hbeg = gc0 * rep, hend = gc1 * rep;
+    } else {
+        gc0 = gsel * a.gp, gc1 = min(G, gc0 + a.gp);
+        if (a.talk)
+            hbeg = 0, hend = H;
+        else
+            hbeg = gc0 * rep, hend = gc1 * rep;
+    }
+    const int rows = (hend - hbeg) * QT, Rg = rep * QT;
+    const int dkp = a.dkp, dvp = a.dvp, KS = dkp + 4;
+    const Layout L = mix_layout(rows, dkp, dvp, H, APPLY, a.talk != nullptr);
+    float* qs = sm + L.q;
+    float* kv = sm + L.kv;
+    float* Pm = sm + L.p;
+    float* Wm = a.talk ? sm + L.w : Pm;
+    float* talk_s = sm + L.talk;
+    float* Mr = sm + L.m;
+    float* Lr = sm + L.l;
+    long long* rowoff = reinterpret_cast<long long*>(sm + L.off);
+    const int M = a.ix.M;
+    const int p0 = a.ix.positions[q_beg], p1 = p0 + nq - 1;
+    const int kmin = chunk > 0 ? (p0 / chunk) * chunk : 0;
+    const int ntile = (p1 - kmin) / KT + 1;
+    const int per = (ntile + a.shares - 1) / a.shares;
+    const int t0 = share * per, t1 = min(ntile, t0 + per);
+    const int slot = a.seq_slot[b];
+    const T* pool = static_cast<const T*>(a.cache.pool);
+    const int row_elems = G * (dk + dv), psz = a.cache.page_size;
+
+    // queries of the CTA's heads: row (h - hbeg) * QT + i, zero padded
+    for (int idx = tid; idx < rows * dkp; idx += NT) {
+        const int row = idx / dkp, d = idx - row * dkp;
+        const int h = hbeg + row / QT, i = row % QT;
+        qs[idx] = (i < nq && d < dk) ? a.q[(long long)(q_beg + i) * a.ldq + (long long)h * dk + d] : 0.f;
+    }
+    if (APPLY) {
+        if (a.talk)
+            for (int i = tid; i < H * H; i += NT) talk_s[i] = a.talk[i];
+        for (int row = tid; row < rows; row += NT) {   // final statistics: the key shares' maxima and sums merged
+            const int h = hbeg + row / QT, i = row % QT;
+            float mm = -INFINITY, ll = 0.f;
+            if (i < nq) {
+                const long long at = (long long)(q_beg + i) * H + h;
+                for (int s = 0; s < a.shares; ++s) mm = fmaxf(mm, a.stats[(long long)s * M * H + at]);
+                for (int s = 0; s < a.shares; ++s) {
+                    const float ms = a.stats[(long long)s * M * H + at];
+                    if (ms > -INFINITY) ll += a.stats[(long long)(a.shares + s) * M * H + at] * expf(ms - mm);
+                }
+            }
+            Mr[row] = mm > -INFINITY ? mm : 0.f;
+            Lr[row] = ll > 0.f ? 1.f / ll : 0.f;
+        }
+    }
+    float mrun[4][2], lrun[4][2];
+    float o[SLOTS][CB][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) mrun[r][x] = -INFINITY, lrun[r][x] = 0.f;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s)
+#pragma unroll
+        for (int c = 0; c < CB; ++c)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[s][c][e] = 0.f;
+
+    const int sc0 = (APPLY && a.talk) ? 0 : gc0, sc1 = (APPLY && a.talk) ? G : gc1;   // groups whose scores are needed
+    for (int t = t0; t < t1; ++t) {
+        const int kb = kmin + t * KT;
+        const int nk = min(KT, p1 - kb + 1);
+        __syncthreads();
+        if (tid < KT) {
+            long long off = 0;
+            if (tid < nk) {
+                const int j = kb + tid;
+                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
+                off = ((long long)page * psz + j % psz) * row_elems;
+            }
+            rowoff[tid] = off;
+        }
+        for (int c = sc0; c < sc1; ++c) {
+            __syncthreads();
+            load_tile<T>(pool, rowoff, nk, c * dk, dk, dkp, KS, kv, a.vec);
+            __syncthreads();
+            const int lrow0 = (c * rep - hbeg) * QT;   // first CTA row of this group
+#pragma unroll
+            for (int rc = 0; rc < 4; ++rc) {
+                if (rc * 32 >= Rg) break;
+                const int rg0 = rc * 32 + ty, rg1 = rg0 + 16;
+                const float* qa = qs + (size_t)(lrow0 + min(rg0, Rg - 1)) * dkp;
+                const float* qb = qs + (size_t)(lrow0 + min(rg1, Rg - 1)) * dkp;
+                float acc[2][4];
+#pragma unroll
+                for (int x = 0; x < 2; ++x)
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) acc[x][y] = 0.f;
+                for (int d = 0; d < dkp; d += 4) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(qa + d);
+                    const float4 a1 = *reinterpret_cast<const float4*>(qb + d);
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) {
+                        const float4 kk = *reinterpret_cast<const float4*>(kv + (size_t)(tx + 16 * y) * KS + d);
+                        acc[0][y] = fmaf(a0.x, kk.x, acc[0][y]);
+                        acc[0][y] = fmaf(a0.y, kk.y, acc[0][y]);
+                        acc[0][y] = fmaf(a0.z, kk.z, acc[0][y]);
+                        acc[0][y] = fmaf(a0.w, kk.w, acc[0][y]);
+                        acc[1][y] = fmaf(a1.x, kk.x, acc[1][y]);
+                        acc[1][y] = fmaf(a1.y, kk.y, acc[1][y]);
+                        acc[1][y] = fmaf(a1.z, kk.z, acc[1][y]);
+                        acc[1][y] = fmaf(a1.w, kk.w, acc[1][y]);
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int rg = x ? rg1 : rg0;
+                    const bool row_ok = rg < Rg;
+                    const int hh = row_ok ? rg / QT : 0, i = row_ok ? rg % QT : 0;
+                    const int h = c * rep + hh, pos = p0 + i;
+                    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+                    float s[4];
+                    float tmax = -INFINITY;
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) {
+                        const int jj = tx + 16 * y, j = kb + jj;
+                        const bool ok = row_ok && i < nq && jj < nk && j <= pos && j >= lo;
+                        float v = acc[x][y] * a.d.scale;
+                        if (a.dist_bias && ok) v += a.dist_bias[(long long)min(pos - j, a.far) * H + h];
+                        s[y] = ok ? v : -INFINITY;
+                        tmax = fmaxf(tmax, s[y]);
+                    }
+                    if (!APPLY) {
+#pragma unroll
+                        for (int w = 8; w > 0; w >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, w));
+                        const float mnew = fmaxf(mrun[rc][x], tmax);
+                        float sum = 0.f;
+                        if (mnew > -INFINITY) {
+#pragma unroll
+                            for (int y = 0; y < 4; ++y) sum += s[y] > -INFINITY ? expf(s[y] - mnew) : 0.f;
+                        }
+#pragma unroll
+                        for (int w = 8; w > 0; w >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+                        if (mnew > -INFINITY) {
+                            const float keep = mrun[rc][x] > -INFINITY ? expf(mrun[rc][x] - mnew) : 0.f;
+                            lrun[rc][x] = lrun[rc][x] * keep + sum;
+                            mrun[rc][x] = mnew;
+                        }
+                    } else if (row_ok) {
+                        const int lrow = lrow0 + rg;
+                        const float mm = Mr[lrow], il = Lr[lrow];
+#pragma unroll
+                        for (int y = 0; y < 4; ++y)
+                            Pm[(size_t)lrow * PS + tx + 16 * y] = s[y] > -INFINITY ? expf(s[y] - mm) * il : 0.f;
+                    }
+                }
+            }
+        }
+        if (!APPLY) continue;
+        __syncthreads();
+        if (a.talk) {   // w'_h = sum_g talk[h][g] w_g for the heads whose values this CTA multiplies
+            const int h0 = gc0 * rep, h1 = gc1 * rep;
+            for (int idx = tid; idx < QT * KT; idx += NT) {
+                const int i = idx / KT, j = idx - i * KT;
+                for (int h = h0; h < h1; ++h) {
+                    float acc = 0.f;
+                    for (int g = 0; g < H; ++g) acc = fmaf(talk_s[h * H + g], Pm[(size_t)(g * QT + i) * PS + j], acc);
+                    Wm[(size_t)(h * QT + i) * PS + j] = acc;
+                }
+            }
+        }
+        for (int c = gc0; c < gc1; ++c) {
+            __syncthreads();
+            load_tile<T>(pool, rowoff, nk, G * dk + c * dv, dv, dvp, dvp, kv, a.vec);
+            __syncthreads();
+            const int cl = c - gc0;
+            const int lrow0 = (c * rep - hbeg) * QT;
+            const float* wrow[SLOTS];
+            bool active[SLOTS];
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                const int rg = ty + 16 * (s % a.rag);
+                active[s] = (s / a.rag == cl) && rg < Rg;
+                wrow[s] = Wm + (size_t)(lrow0 + (active[s] ? rg : 0)) * PS;
+            }
+            const bool col1 = CB > 1 && (64 + tx * 4) < dvp;
+            const bool col0 = tx * 4 < dvp;
+            for (int j = 0; j < nk; ++j) {
+                float4 v[CB];
+                v[0] = col0 ? *reinterpret_cast<const float4*>(kv + (size_t)j * dvp + tx * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (CB > 1)
+                    v[CB - 1] = col1 ? *reinterpret_cast<const float4*>(kv + (size_t)j * dvp + 64 + tx * 4)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) {
+                    if (!active[s]) continue;
+                    const float w = wrow[s][j];
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb) {
+                        o[s][cb][0] = fmaf(w, v[cb].x, o[s][cb][0]);
+                        o[s][cb][1] = fmaf(w, v[cb].y, o[s][cb][1]);
+                        o[s][cb][2] = fmaf(w, v[cb].z, o[s][cb][2]);
+                        o[s][cb][3] = fmaf(w, v[cb].w, o[s][cb][3]);
+                    }
+                }
+            }
+        }
+    }
+
+    if (!APPLY) {
+        if (tx == 0) {
+#pragma unroll
+            for (int rc = 0; rc < 4; ++rc)
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int rg = rc * 32 + ty + 16 * x;
+                    if (rg >= Rg) continue;
+                    const int hh = rg / QT, i = rg % QT;
+                    if (i >= nq) continue;
+                    const long long at = (long long)(q_beg + i) * H + gc0 * rep + hh;
+                    a.stats[(long long)share * M * H + at] = mrun[rc][x];
+                    a.stats[(long long)(a.shares + share) * M * H + at] = lrun[rc][x];
+                }
+        }
+        return;
+    }
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const int cl = s / a.rag, c = gc0 + cl, rg = ty + 16 * (s % a.rag);
+        if (c >= gc1 || rg >= Rg) continue;
+        const int hh = rg / QT, i = rg % QT, h = c * rep + hh;
+        if (i >= nq) continue;
+        const int m = q_beg + i;
+        float gate = 1.f;
+        if (a.shares == 1 && a.gate) gate = 1.f / (1.f + expf(-a.gate[(long long)m * a.ldg + h]));
+#pragma unroll
+        for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = cb * 64 + tx * 4 + e;
+                if (col >= dv) continue;
+                if (a.shares == 1)
+                    stx(a.out, (long long)m * a.ldo + (long long)h * dv + col, a.of32, o[s][cb][e] * gate);
+                else
+                    a.part[((long long)share * M + m) * H * dv + (long long)h * dv + col] = o[s][cb][e];
+            }
+    }
+}
+
+// out[m][h][:] = sigmoid(gate[m][h]) * sum over the key shares (in index order) of their partial results
+__global__ void mix_merge_kernel(const float* part, int shares, int M, int H, int dv, const float* gate, long long ldg,
+                                 void* out, int of32, long long ldo) {
+    const int m = blockIdx.x, n = H * dv;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < shares; ++s) acc += part[((long long)s * M + m) * n + e];
+        const int h = e / dv;
+        if (gate) acc *= 1.f / (1.f + expf(-gate[(long long)m * ldg + h]));
+        stx(out, (long long)m * ldo + e, of32, acc);
+    }
+}
+
+// dynamic shared memory: the row (n floats) + per-head sums of squares and factors
+template <typename T>
+__global__ void mix_post_kernel(SeqIndex ix, float* qkv, long long ld, MixDims d, MixPost p, PagedRows cache) {
+    extern __shared__ float sm[];
+    const int H = d.heads, G = d.kv_heads, dk = d.dk, dv = d.dv;
+    const int nq = H * dk, nk = G * dk, nv = G * dv, n = nq + nk + nv, units = H + 2 * G;
+    float* row = sm;
+    float* fac = sm + n;
+    const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    float* src = qkv + (long long)m * ld;
+    for (int i = tid; i < n; i += blockDim.x) row[i] = src[i] + (p.bias ? p.bias[i] : 0.f);
+    __syncthreads();
+    // sum of squares of every query head, key head and value head
+    for (int u = warp; u < units; u += nw) {
+        const int beg = u < H ? u * dk : (u < H + G ? nq + (u - H) * dk : nq + nk + (u - H - G) * dv);
+        const int len = u < H + G ? dk : dv;
+        float ss = 0.f;
+        for (int i = lane; i < len; i += 32) ss += row[beg + i] * row[beg + i];
+        ss = warp_sum(ss);
+        if (lane == 0) fac[u] = ss;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int pos = ix.positions[m];
+        const float temp = p.temp_every > 0 ? 1.f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.f) : 1.f;
+        float wq = 0.f, wk = 0.f;
+        if (p.norm_whole) {
+            for (int u = 0; u < H; ++u) wq += fac[u];
+            for (int u = 0; u < G; ++u) wk += fac[H + u];
+            wq = 1.f / sqrtf(wq / (float)nq + p.eps), wk = 1.f / sqrtf(wk / (float)nk + p.eps);
+        }
+        for (int u = 0; u < H; ++u) {
+            float f = !p.q_norm ? 1.f : (p.norm_whole ? wq : 1.f / sqrtf(fac[u] / (float)dk + p.eps));
+            f *= temp;
+            if (p.head_factor) f *= p.head_factor[u];
+            fac[u] = f;
+        }
+        for (int u = 0; u < G; ++u)
+            fac[H + u] = !p.k_norm ? 1.f : (p.norm_whole ? wk : 1.f / sqrtf(fac[H + u] / (float)dk + p.eps));
+        for (int u = 0; u < G; ++u) fac[H + G + u] = p.v_unit ? 1.f / sqrtf(fac[H + G + u] / (float)dv + p.eps) : 1.f;
+    }
+    __syncthreads();
+    const int pos = ix.positions[m], slot = ix.token_slot[m];
+    const int page = cache.page_table[(long long)slot * cache.max_pages + pos / cache.page_size];
+    T* dst = static_cast<T*>(cache.pool) + ((long long)page * cache.page_size + pos % cache.page_size) * (nk + nv);
+    for (int i = tid; i < n; i += blockDim.x) {
+        if (i < nq) {
+            const float w = p.q_norm ? p.q_norm[p.norm_whole ? i : i % dk] : 1.f;
+            src[i] = row[i] * fac[i / dk] * w;
+        } else if (i < nq + nk) {
+            const int e = i - nq;
+            const float w = p.k_norm ? p.k_norm[p.norm_whole ? e : e % dk] : 1.f;
+            stf(dst + e, row[i] * fac[H + e / dk] * w);
+        } else {
+            const int e = i - nq - nk;
+            stf(dst + nk + e, row[i] * fac[H + G + e / dv]);
+        }
+    }
+}
+
+}  // namespace
+
+int launch_mix_post(const SeqIndex& ix, float* qkv, long long ld, const MixDims& d, const MixPost& p,
+                    const PagedRows& cache, cudaStream_t stream) {
+    if (ix.M <= 0) return 0;
+    const int n = d.heads * d.dk + d.kv_heads * (d.dk + d.dv), units = d.heads + 2 * d.kv_heads;
+    const size_t smem = (size_t)(n + units) * sizeof(float);
+    if (smem > 200 * 1024) return set_error("mix_post: a row of %d values does not fit shared memory", n);
+    static PerDeviceOnce once;
+    if (once.need()) {
+        ASD_CUDA(cudaFuncSetAttribute(mix_post_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        ASD_CUDA(cudaFuncSetAttribute(mix_post_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    }
+    if (cache.f32)
+        mix_post_kernel<float><<<ix.M, 128, smem, stream>>>(ix, qkv, ld, d, p, cache);
+    else
+        mix_post_kernel<__nv_bfloat16><<<ix.M, 128, smem, stream>>>(ix, qkv, ld, d, p, cache);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <typename T, bool APPLY, int CB>
+static int launch_one(const MixArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
+    static PerDeviceOnce once;
+    if (once.need())
+        ASD_CUDA(cudaFuncSetAttribute(mix_attn_kernel<T, APPLY, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    mix_attn_kernel<T, APPLY, CB><<<grid, NT, smem, stream>>>(a);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int mix_attention_check(const MixDims& d, int talk) {
+    if (d.heads <= 0 || d.kv_heads <= 0 || d.heads % d.kv_heads || d.dk <= 0 || d.dv <= 0 || d.chunk < 0)
+        return set_error("mixed attention: bad sizes");
+    if (d.dv > 128) return set_error("mixed attention: value size %d above 128", d.dv);
+    if (d.dk > 512) return set_error("mixed attention: key size %d above 512", d.dk);
+    if (d.heads / d.kv_heads > MAX_ROWS) return set_error("mixed attention: more than %d query heads per key head", MAX_ROWS);
+    if (talk && d.heads > 64) return set_error("mixed attention: more than 64 heads with mixed weights");
+    return 0;
+}
+
+int launch_mix_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slot, int nseq, int max_qlen, int max_kv_len,
+                         const float* q, long long ldq, const MixDims& d, const float* dist_bias, int far,
+                         const float* talk, const float* gate, long long ldg, const PagedRows& cache, void* out, int of32,
+                         long long ldo, const MixWork& ws, cudaStream_t stream) {
+    if (ix.M <= 0 || nseq <= 0) return 0;
+    if (mix_attention_check(d, talk != nullptr)) return -1;
+    const int H = d.heads, G = d.kv_heads, rep = H / G;
+    const int dkp = (d.dk + 3) & ~3, dvp = (d.dv + 3) & ~3;
+    MixArgs a;
+    a.ix = ix, a.cu_q = cu_q, a.seq_slot = seq_slot, a.q = q, a.ldq = ldq, a.d = d, a.dist_bias = dist_bias, a.far = far;
+    a.talk = talk, a.gate = gate, a.ldg = ldg, a.cache = cache, a.out = out, a.of32 = of32, a.ldo = ldo;
+    a.stats = ws.stats, a.part = ws.part, a.dkp = dkp, a.dvp = dvp;
+    a.vec = (d.dk % 4 == 0 && d.dv % 4 == 0) ? 1 : 0;
+    // key/value groups per apply CTA and queries per tile: the CTA's (head, query) pairs, the result rows a thread
+    // holds and shared memory must fit
+    const int want_qt = max_qlen >= 16 ? 16 : (max_qlen >= 8 ? 8 : (max_qlen >= 4 ? 4 : (max_qlen >= 2 ? 2 : 1)));
+    int gp = talk ? G : 1, QT = 0;
+    size_t smem_apply = 0;
+    for (; gp >= 1 && !QT; gp = (gp + 1) / 2) {
+        for (int qt = want_qt; qt >= 1; qt >>= 1) {
+            const int rows = (talk ? H : gp * rep) * qt, rag = (rep * qt + 15) / 16;
+            const size_t sm = (size_t)mix_layout(rows, dkp, dvp, H, true, talk != nullptr).total * sizeof(float);
+            if (rows <= MAX_ROWS && rep * qt <= MAX_ROWS && gp * rag <= SLOTS && sm <= 200 * 1024) {
+                QT = qt, smem_apply = sm;
+                break;
+            }
+        }
+        if (QT || gp == 1) break;
+    }
+    if (!QT) return set_error("mixed attention: %d heads of %d + %d values do not fit a CTA", H, d.dk, d.dv);
+    a.QT = QT, a.gp = gp, a.rag = (rep * QT + 15) / 16;
+    const int tiles = (max_qlen + QT - 1) / QT, ngroups = (G + gp - 1) / gp;
+    // steps of few tokens: cut the keys into shares so that the CTAs cover the SMs
+    int shares = 1;
+    const long long base = (long long)tiles * nseq * ngroups;
+    const int key_tiles = (max_kv_len + KT - 1) / KT;
+    if (base < 148 && ws.stats && ws.part) {
+        shares = (int)std::min<long long>((296 + base - 1) / base, (long long)std::max(1, key_tiles / 2));
+        shares = std::min(shares, 32);
+        while (shares > 1 && ((long long)shares * ix.M * H * d.dv > ws.part_elems ||
+                              (long long)2 * shares * ix.M * H > ws.stats_elems))
+            --shares;
+    }
+    if ((long long)2 * shares * ix.M * H > ws.stats_elems || !ws.stats)
+        return set_error("mixed attention: statistics workspace too small");
+    a.shares = shares;
+    const size_t smem_stats = (size_t)mix_layout(rep * QT, dkp, dvp, H, false, false).total * sizeof(float);
+    const dim3 gs(tiles, nseq, shares * G), ga(tiles, nseq, shares * ngroups);
+    const bool wide = dvp > 64;
+    int rc;
+    if (cache.f32) {
+        rc = launch_one<float, false, 1>(a, gs, smem_stats, stream);
+        if (!rc) rc = wide ? launch_one<float, true, 2>(a, ga, smem_apply, stream) : launch_one<float, true, 1>(a, ga, smem_apply, stream);
+    } else {
+        rc = launch_one<__nv_bfloat16, false, 1>(a, gs, smem_stats, stream);
+        if (!rc)
+            rc = wide ? launch_one<__nv_bfloat16, true, 2>(a, ga, smem_apply, stream)
+                      : launch_one<__nv_bfloat16, true, 1>(a, ga, smem_apply, stream);
+    }
+    if (rc) return rc;
+    if (shares > 1) {
+        mix_merge_kernel<<<ix.M, 128, 0, stream>>>(ws.part, shares, ix.M, H, d.dv, gate, ldg, out, of32, ldo);
+        count_launch(1);
+        ASD_CUDA(cudaGetLastError());
+    }
+    return 0;
+}
+
+}  // namespace asd

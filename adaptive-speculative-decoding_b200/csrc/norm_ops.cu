@@ -102,15 +102,24 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 }
 
 // out[r][f] = gelu_tanh(z[r][f]) (mode 0, z rows of F floats) or silu(z[r][f]) * z[r][F + f] (mode 1, rows of 2 F)
-__global__ void ff_act_kernel(const float* z, void* out, int of32, long long n, int F, int mode) {
+// mode 2: relu(z[r][f])^2.  bias (optional) is added to z first: [F], or [2 F] in mode 1.
+__global__ void ff_act_kernel(const float* z, void* out, int of32, long long n, int F, int mode, const float* bias) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    if (mode == 0) {
-        stx(out, i, of32, gelu_tanh_f(z[i]));
+    if (mode != 1) {
+        float v = z[i];
+        if (bias) v += bias[(int)(i % F)];
+        if (mode == 0) {
+            stx(out, i, of32, gelu_tanh_f(v));
+        } else {
+            v = fmaxf(v, 0.f);
+            stx(out, i, of32, v * v);
+        }
     } else {
         const long long r = i / F;
         const int f = (int)(i - r * F);
-        const float g = z[r * 2 * F + f], u = z[r * 2 * F + F + f];
+        float g = z[r * 2 * F + f], u = z[r * 2 * F + F + f];
+        if (bias) g += bias[f], u += bias[F + f];
         stx(out, i, of32, g / (1.f + expf(-g)) * u);
     }
 }
@@ -200,12 +209,13 @@ int launch_embed_normed(const SeqIndex& ix, const void* embed, int wf32, const f
     return 0;
 }
 
-int launch_ff_act(const float* z, void* out, int of32, long long rows, int F, int gated, cudaStream_t stream) {
+int launch_ff_act(const float* z, void* out, int of32, long long rows, int F, int gated, cudaStream_t stream,
+                  const float* bias) {
     const long long n = rows * F;
     if (n <= 0) return 0;
     const long long blocks = (n + 255) / 256;
     if (blocks > 0x7fffffffLL) return set_error("ff_act: too many elements");
-    ff_act_kernel<<<(unsigned)blocks, 256, 0, stream>>>(z, out, of32, n, F, gated ? 1 : 0);
+    ff_act_kernel<<<(unsigned)blocks, 256, 0, stream>>>(z, out, of32, n, F, gated, bias);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;

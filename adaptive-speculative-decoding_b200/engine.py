@@ -10,7 +10,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ._lib import (AsdError, MavipelConfigC, MavipelLayerC, MezilixConfigC, MezilixLayerC, ModelConfigC, RivetarConfigC,
+from ._lib import (AsdError, LukopelConfigC, LukopelLayerC, MavipelConfigC, MavipelLayerC, MezilixConfigC, MezilixLayerC, ModelConfigC, RivetarConfigC,
                    RivetarLayerC, check, lib)
 from .models.qwen2 import Qwen2Config, pack_layer, random_packed_layer
 from .ops import NUM_FEATURES
@@ -760,6 +760,37 @@ class MavipelEngine(RivetarEngine):
                                    min(l.window, 1 << 30), l.r_heads, l.r_dim, l.r_decay_rank, self.FF_CODE[l.ff_kind], l.ff,
                                    l.experts, l.top, l.expert_ff, l.shared_ff, l.rot_base, l.scale, l.softcap,
                                    l.left_scale, l.right_scale)
+        return c, arr
+
+
+class LukopelEngine(RivetarEngine):
+    """One Lukopel-family model on one GPU: wraps an ``asd_lukopel_engine_t`` handle.  Same ownership as
+    ``RivetarEngine``: per layer EXECUTION the paged key/value cache of its attention mixer (``PageTable``); nothing else
+    is carried between forwards (the residual streams live inside one forward).  Same ``forward`` interface as
+    ``QwenEngine``, so ``SpecDecoder``, ``Stage`` and the trace runner drive it unchanged."""
+
+    PREFIX = "lukopel"
+    PROFILE_CLASSES = ("dense", "attention", "activation", "glue", "lm_head")
+
+    @staticmethod
+    def _family():
+        from .models import lukopel
+        return lukopel
+
+    def _c_config(self, cfg, max_tokens: int, page_size: int, dtype):
+        loop = cfg.loop or (0, 0, 0)
+        c = LukopelConfigC(cfg.width, cfg.vocab_size, cfg.num_hidden_layers, cfg.eps, cfg.embed_scale, cfg.n_streams,
+                           cfg.max_positions, loop[0], loop[1], loop[2], max_tokens, page_size, self.ring,
+                           1 if dtype == torch.float32 else 0)
+        arr = (LukopelLayerC * max(1, cfg.num_hidden_layers))()
+        for i, l in enumerate(cfg.layers):
+            full = l.type == "attention"
+            if full and l.bias_rows <= 0:
+                raise AsdError(f"layer {i}: the size of the distance-bias table is unknown (a checkpoint's tensor shapes "
+                               "give it: LukopelConfig.with_shapes)")
+            arr[i] = LukopelLayerC(l.heads, l.kv_heads, l.dim, l.vdim, 0 if full else 1, 1 if full else 0,
+                                   1 if full else 0, l.chunk, l.far if full else 0, l.temp_every if full else 0,
+                                   1 if l.ff_kind else 0, l.ff, l.scale, l.temp_coef if full else 0.0)
         return c, arr
 
 

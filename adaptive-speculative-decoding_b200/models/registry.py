@@ -1,6 +1,6 @@
 """Model registry: which configuration class, engine class and library components serve a checkpoint.
 
-A checkpoint directory is recognised by its ``config.json``: ``"architecture": "Mezilix"`` / ``"Rivetar"`` / ``"Mavipel"`` or the Hugging Face keys
+A checkpoint directory is recognised by its ``config.json``: ``"architecture": "Mezilix"`` / ``"Rivetar"`` / ``"Mavipel"`` / ``"Lukopel"`` or the Hugging Face keys
 ``architectures`` / ``model_type`` of the Qwen2 family (what the reference hands to vLLM,
 src/serving/real_model_pipeline.py:98-108).  ``Stage``, the trace runner and ``bench.py`` all go through here."""
 from __future__ import annotations
@@ -45,6 +45,11 @@ def _mavipel_cfg(d: dict, name: str = "mavipel"):
     return MavipelConfig.from_dict(d, name=name)
 
 
+def _lukopel_cfg(d: dict, name: str = "lukopel"):
+    from .lukopel import LukopelConfig
+    return LukopelConfig.from_dict(d, name=name)
+
+
 def _qwen_engine():
     from ..engine import QwenEngine
     return QwenEngine
@@ -65,11 +70,17 @@ def _mavipel_engine():
     return MavipelEngine
 
 
+def _lukopel_engine():
+    from ..engine import LukopelEngine
+    return LukopelEngine
+
+
 FAMILIES: Dict[str, Family] = {
     "qwen2": Family("qwen2", ("linear", "qwen", "sampling"), ("bfloat16",), _qwen_cfg, _qwen_engine),
     "mezilix": Family("mezilix", ("mezilix",), ("bfloat16", "float32"), _mezilix_cfg, _mezilix_engine),
     "rivetar": Family("rivetar", ("rivetar",), ("bfloat16", "float32"), _rivetar_cfg, _rivetar_engine),
     "mavipel": Family("mavipel", ("mavipel",), ("bfloat16", "float32"), _mavipel_cfg, _mavipel_engine),
+    "lukopel": Family("lukopel", ("lukopel",), ("bfloat16", "float32"), _lukopel_cfg, _lukopel_engine),
 }
 
 

@@ -204,7 +204,7 @@ class Stage:
                 # the carried-state rings must cover the k + 1 positions a verify step may re-feed
                 self.engine = self.family.engine()(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len,
                                                    max_tokens=mt, device=f"cuda:{self.gpu_ids[0]}", ring=max(8, k + 2))
-            elif self.family.name in ("rivetar", "mavipel"):
+            elif self.family.name in ("rivetar", "mavipel", "lukopel"):
                 # the recurrent-state ring must cover the positions a draft / verify step may re-feed
                 self.engine = self.family.engine()(self.cfg, max_seqs=max_batch, max_seq_len=max_model_len,
                                                    max_tokens=mt, device=f"cuda:{self.gpu_ids[0]}", ring=max(2, k + 2))

@@ -72,7 +72,7 @@ def build_engine(model_dir: str, dtype: str, max_tokens: int, device="cuda"):
         return fam, None
     Engine = fam.engine()
     max_tokens = max(int(max_tokens), 1)
-    if fam.name in ("mezilix", "rivetar", "mavipel"):
+    if fam.name in ("mezilix", "rivetar", "mavipel", "lukopel"):
         page = 16
         pages = (max_tokens + page - 1) // page + 8          # every live request may leave a last page part empty
         eng = Engine(cfg, max_seqs=8, max_seq_len=max_tokens, max_tokens=min(1024, max_tokens), page_size=page,

@@ -473,6 +473,71 @@ ASD_API int asd_mavipel_forward(asd_mavipel_engine_t* e, const int32_t* tokens, 
 ASD_API int asd_mavipel_profile_read(asd_mavipel_engine_t* e, float* ms_by_class, int* launches_by_class, int nclass);
 ASD_API int asd_mavipel_device_error(asd_mavipel_engine_t* e);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Lukopel family engine (lukopel_engine.cu).  x = embed[token] * embed_scale + pos[position]; a token carries `streams`
+ * residual streams, all equal to x at the start.  Sublayer q of a layer (1 mixer, 2 feed-forward) reads
+ * u = sum_s hc<q>_read[s] x_s, computes y = sublayer(u / rms(u) * norm<q>) and writes all streams at once from the old
+ * ones, x_t <- sum_s hc<q>_mix[s][t] x_s + hc<q>_write[t] y.  A layer without these weights reads the plain sum and
+ * adds y (with one stream: the ordinary residual).  logits = head . final_norm(sum of the streams).
+ * The mixer is grouped-query softmax attention (heads, kv_heads, dim, vdim; query head h reads key/value head
+ * h / (heads / kv_heads)); its steps are parameters:
+ *   in_bias (tensor)    biases of q | k | v
+ *   norm_whole          0: every query / key head is RMS-normed over dim with weights [dim] shared by the heads;
+ *                       1: the whole query (key) projection is normed at once with weights [heads * dim] ([kv_heads * dim])
+ *   temp_every, temp_coef   queries times 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1)  (temp_every 0: not)
+ *   head_factor (tensor)    queries of head h times head_factor[h]
+ *   v_unit              every value head is divided by its root mean square (eps inside the root) before it is cached
+ *   dist_bias (tensor)  fp32 [far + 1][heads]: added to the score at distance min(i - j, far), after scores * scale
+ *   chunk               0: position i sees every j <= i; else only those with floor(j / chunk) == floor(i / chunk)
+ *   talk (tensor)       fp32 [heads][heads]: softmax weights mixed across the heads, w'_h = sum_g talk[h][g] w_g
+ *   gated               the input projection has `heads` more rows; head h's result is multiplied by their sigmoid
+ *   o_bias (tensor)     bias of the output projection
+ * ff_kind 0: none; 1: W_down relu(W_up h + up_bias)^2 + down_bias.
+ * Layers loop_start .. loop_stop - 1 run loop_times times with the same weights (0: no repeated span); every execution
+ * ("run") has its own cache.  dtype as for the Rivetar engine.  Paged pool: per run [num_pages][page_size][kv_heads *
+ * (dim + vdim)], keys then values, runs back to back.  Nothing else is carried between forwards.
+ */
+typedef struct asd_lukopel_layer_config {
+    int heads, kv_heads, dim, vdim;
+    int norm_whole, v_unit, gated, chunk, far, temp_every;
+    int ff_kind, ff;
+    float scale, temp_coef;
+} asd_lukopel_layer_config;
+typedef struct asd_lukopel_config {
+    int width, vocab, n_layers;
+    float eps, embed_scale;
+    int streams, max_positions;
+    int loop_start, loop_stop, loop_times;
+    int max_tokens, page_size, ring, dtype;
+} asd_lukopel_config;
+typedef struct asd_lukopel_engine asd_lukopel_engine_t;
+
+ASD_API asd_lukopel_engine_t* asd_lukopel_create(const asd_lukopel_config* cfg, const asd_lukopel_layer_config* layers);
+ASD_API void asd_lukopel_destroy(asd_lukopel_engine_t* e);
+/* Weights by name; matrices row-major [out, in] in the engine's dtype, vectors and everything marked fp32 always fp32.
+ * layer -1: "embed" [vocab, width], "pos" [max_positions, width] (engine's dtype; optional), "final_norm" [width],
+ * "head" [vocab, width].  Every layer: "norm1", "w_in" = [q | k | v | gate rows] stacked by rows, "w_o" [width, heads *
+ * vdim], optional "in_bias", "o_bias", "q_norm", "k_norm", "head_factor", "dist_bias", "talk" as above; with ff_kind 1
+ * "norm2", "w_up" [ff, width], "up_bias", "w_down" [width, ff], "down_bias"; optional "hc1_read", "hc1_write" [streams],
+ * "hc1_mix" [streams][streams] (from-stream major) and the same for "hc2_". */
+ASD_API int asd_lukopel_set_tensor(asd_lukopel_engine_t* e, int layer, const char* name, const void* data);
+ASD_API size_t asd_lukopel_cache_bytes(const asd_lukopel_engine_t* e, int num_pages);
+ASD_API size_t asd_lukopel_state_bytes(const asd_lukopel_engine_t* e, int max_seqs);   /* 0: the cache is all */
+ASD_API int asd_lukopel_set_cache(asd_lukopel_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
+                                  int max_seqs, int max_pages_per_seq, float* state);
+/* options: "tc_linear", "tc_min_rows" as for the Mezilix engine; "profile" */
+ASD_API int asd_lukopel_set_option(asd_lukopel_engine_t* e, const char* name, int value);
+/* Same arguments as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
+ * sum of the streams that leaves every layer execution. */
+ASD_API int asd_lukopel_forward(asd_lukopel_engine_t* e, const int32_t* tokens, const int32_t* positions,
+                                const int32_t* token_slot, int M, const int32_t* cu_q, const int32_t* seq_slot, int nseq,
+                                int max_qlen, int max_kv_len, const int32_t* logit_rows, int n_logit_rows,
+                                float* logits_out, long long logits_ld, float* layer_out, void* stream);
+/* ms and launches by kernel class since the last read (nclass >= 5): 0 dense projections, 1 attention, 2 feed-forward
+ * activations, 3 embedding / stream reads and writes / norms / cache append, 4 output head */
+ASD_API int asd_lukopel_profile_read(asd_lukopel_engine_t* e, float* ms_by_class, int* launches_by_class, int nclass);
+ASD_API int asd_lukopel_device_error(asd_lukopel_engine_t* e);
+
 #ifdef __cplusplus
 }
 #endif
