@@ -300,6 +300,9 @@ def pack(w: Dict[str, torch.Tensor], cfg: LukopelConfig, device, dtype) -> Dict[
         out[(i, "w_o")] = mat(w[m + "o"])
         if l.type == "attention":
             out[(i, "w_in")] = mat(cat([m + "q", m + "k", m + "v", m + "g"]))
+            if l.bias_rows < 2 or l.bias_max <= l.bias_rows // 2:
+                raise ValueError(f"layer {i}: a distance-bias table of {l.bias_rows} rows cannot reach its last row at "
+                                 f"distance {l.bias_max}")
             rows = torch.tensor(distance_rows(l.bias_rows, l.bias_max, l.far), dtype=torch.long)
             out[(i, "dist_bias")] = vec(w[m + "rel"].to(torch.float32)[rows])
             out[(i, "talk")] = vec(w[m + "talk"])

@@ -686,6 +686,15 @@ def family_sizes(family="mezilix"):
                                       name=f"rivetar-{label}")
             out.append((label, fm, rv))
             continue
+        if family == "lukopel":
+            from asd_b200.models import lukopel, mavipel
+            layers = 6          # four chunked-attention layers and two with the distance bias and mixed softmax weights
+            fm = lukopel.sized_config(width, layers, heads, vocab=32768, dim=128, chunk=1024, ff=3 * width, streams=4,
+                                      max_positions=8192, name=f"lukopel-{label}")
+            mv = mavipel.sized_config(width, layers, heads, vocab=32768, dim=128, window=1024, ff=3 * width,
+                                      name=f"mavipel-{label}")
+            out.append((label, fm, mv))
+            continue
         if family == "rivetar":
             from asd_b200.models import rivetar
             layers = 6          # two of every mixer: latent attention, gated linear attention, windowed attention
@@ -787,13 +796,39 @@ def mavipel_model(cfg, M, kv_len, nseq):
     return {k: tuple(v) for k, v in cls.items()}
 
 
+def lukopel_model(cfg, M, kv_len, nseq):
+    """algorithmic (FLOPs, bytes) of one forward per kernel class, summed over the layer executions (bf16 engine).
+    Attention: scores and values once per visible key, plus the mix across the heads where a layer has one; bytes = the
+    visible cache rows once per sequence plus the queries and results.  Stream reads and writes count under no class."""
+    D = cfg.width
+    tri = 0.5 if M > nseq else 1.0
+    cls = {k: [0.0, 0.0] for k in ("dense", "attention")}
+    for i, _ in cfg.runs():
+        l = cfg.layers[i]
+        kvw, hv = l.kv_heads * (l.dim + l.vdim), l.heads * l.vdim
+        full = l.type == "attention"
+        n_in = l.heads * l.dim + kvw + (l.heads if full else 0)
+        keys = kv_len if full or not l.chunk else min(l.chunk, kv_len)
+        part = tri          # a prompt's positions see half of their keys on average (of their chunk, where there is one)
+        cls["attention"][0] += 2.0 * M * l.heads * keys * (l.dim + l.vdim + (l.heads if full else 0)) * part
+        cls["attention"][1] += 2.0 * nseq * (kv_len if M > nseq else keys) * kvw + 4.0 * M * l.heads * l.dim + 2.0 * M * hv
+        wd = (n_in + hv) * D
+        act = M * (2 * D + 4 * n_in + 2 * hv + 4 * D)
+        if l.ff_kind:
+            wd += 2 * l.ff * D
+            act += M * (2 * D + 6 * l.ff + 4 * D)
+        cls["dense"][0] += 2.0 * M * wd
+        cls["dense"][1] += 2.0 * wd + act
+    return {k: tuple(v) for k, v in cls.items()}
+
+
 def family_model(cfg, M, kv_len, nseq, peaks):
     """algorithmic FLOPs and bytes of one forward of M tokens (nseq sequences, kv_len keys each) per kernel class"""
     import math
     L = cfg.num_hidden_layers
-    if getattr(cfg, "architecture", None) in ("Rivetar", "Mavipel"):
+    if getattr(cfg, "architecture", None) in ("Rivetar", "Mavipel", "Lukopel"):
         L = 1           # these models already sum over the layer executions
-        cls = (rivetar_model if cfg.architecture == "Rivetar" else mavipel_model)(cfg, M, kv_len, nseq)
+        cls = {"Rivetar": rivetar_model, "Mavipel": mavipel_model, "Lukopel": lukopel_model}[cfg.architecture](cfg, M, kv_len, nseq)
         head = (2.0 * nseq * cfg.vocab_size * cfg.width, 2.0 * cfg.vocab_size * cfg.width)
     elif getattr(cfg, "architecture", None) == "Mezilix":
         l, D = cfg.layers[0], cfg.width
@@ -824,16 +859,18 @@ def family_model(cfg, M, kv_len, nseq, peaks):
 
 
 def run_family(args):
-    """--family mezilix | rivetar | mavipel: prefill and decode throughput of that family's engine at layer sizes of real
-    models, beside the Qwen2 engine at the same width, depth, head count and active weights per layer (Mavipel: beside
-    the Rivetar engine at the same width, depth and head count); random weights, synthetic tokens.
+    """--family mezilix | rivetar | mavipel | lukopel: prefill and decode throughput of that family's engine at layer sizes
+    of real models, beside the Qwen2 engine at the same width, depth, head count and active weights per layer (Mavipel:
+    beside the Rivetar engine, Lukopel: beside the Mavipel engine, at the same width, depth and head count); random
+    weights, synthetic tokens.
     Per kernel class: device time (CUDA events around every launch) against its floor = max(FLOPs / measured cuBLAS bf16
     rate, bytes / measured copy bandwidth).  Prints one JSON object; the default workload of this file is untouched."""
     import torch
     import asd_b200  # noqa: F401
-    from asd_b200.engine import MavipelEngine, MezilixEngine, QwenEngine, RivetarEngine
+    from asd_b200.engine import LukopelEngine, MavipelEngine, MezilixEngine, QwenEngine, RivetarEngine
     from asd_b200.models import registry
-    engines = {"mezilix": MezilixEngine, "rivetar": RivetarEngine, "mavipel": MavipelEngine, "qwen2": QwenEngine}
+    engines = {"mezilix": MezilixEngine, "rivetar": RivetarEngine, "mavipel": MavipelEngine, "lukopel": LukopelEngine,
+               "qwen2": QwenEngine}
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     peaks = json.load(open(path)) if os.path.exists(path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     dev = torch.device("cuda", 0)
@@ -933,8 +970,9 @@ def main():
     ap.add_argument("--no-fuse-norm", action="store_true", help="separate add+RMSNorm kernels instead of the fused epilogues")
     ap.add_argument("--nccl-only", action="store_true", help="TP boundaries through ncclAllReduce instead of the fused kernel")
     ap.add_argument("--opt", action="append", help="engine option name=value (e.g. pdl=0, attn_impl=0)")
-    ap.add_argument("--family", default=None, choices=["mezilix", "rivetar", "mavipel"],
-                    help="instead of the default workload: prefill / decode throughput of this model family beside Qwen2 at equal size")
+    ap.add_argument("--family", default=None, choices=["mezilix", "rivetar", "mavipel", "lukopel"],
+                    help="instead of the default workload: prefill / decode throughput of this model family beside its closest "
+                         "existing family at equal size")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -68,13 +68,12 @@ def distance_bucket(n: int, rows: int, far: int) -> int:
 
 
 def distance_bias(T: int, table, far: int):
-    """table [rows, H] -> bias [H, T, T] for i >= j (zero elsewhere; masked anyway)"""
+    """table [rows, H] -> bias [H, T, T]: entry (i, j) is the row of distance i - j (entries with j > i are masked later)"""
     rows, H = table.shape
-    out = torch.zeros(H, T, T, dtype=table.dtype)
-    for i in range(T):
-        for j in range(i + 1):
-            out[:, i, j] = table[distance_bucket(i - j, rows, far)]
-    return out
+    row_of = torch.tensor([distance_bucket(n, rows, far) for n in range(T)])
+    i = torch.arange(T)
+    dist = (i[:, None] - i[None, :]).clamp(min=0)
+    return table[row_of[dist]].permute(2, 0, 1)
 
 
 def query_temperature(T: int, coef: float, every: int):
@@ -172,3 +171,67 @@ def forward(tokens: List[int], w: Dict[str, torch.Tensor], cfg: dict, dtype=torc
             layers_out.append(xs.sum(0))
     x = xs.sum(0)
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+# ------------------------------------------------------------------------------------------------ test models
+def tensor_shapes(cfg: dict, rel_rows=10) -> Dict[str, tuple]:
+    """every tensor of a checkpoint with this configuration; rel_rows: rows of the distance-bias tables (one number, or
+    one per layer), which no configuration key gives"""
+    D, V = cfg["width"], cfg["vocab"]
+    hyper = "streams" in cfg
+    S = cfg.get("streams", 1)
+    s = {"embed": (V, D), "pos": (cfg["max_positions"], D), "final.norm": (D,), "head": (V, D)}
+    for i, e in enumerate(cfg["layers"]):
+        p, mx, m = f"l{i}.", f"l{i}.mix.", e["mixer"]
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        s[p + "norm1"] = (D,)
+        s.update({mx + "q": (H * dk, D), mx + "k": (G * dk, D), mx + "v": (G * dv, D), mx + "o": (D, H * dv)})
+        if e["type"] == "attention":
+            rows = rel_rows[i] if isinstance(rel_rows, (list, tuple)) else rel_rows
+            s.update({mx + "q.norm": (dk,), mx + "k.norm": (dk,), mx + "rel": (rows, H), mx + "talk": (H, H),
+                      mx + "g": (H, D)})
+        else:
+            s.update({mx + "q.b": (H * dk,), mx + "k.b": (G * dk,), mx + "v.b": (G * dv,), mx + "o.b": (D,),
+                      mx + "q.norm": (H * dk,), mx + "k.norm": (G * dk,), mx + "temp": (H,)})
+        subs = [1]
+        if e.get("mlp") is not None:
+            F = e["mlp"]["ff"]
+            s.update({p + "norm2": (D,), p + "mlp.up": (F, D), p + "mlp.up.b": (F,), p + "mlp.down": (D, F),
+                      p + "mlp.down.b": (D,)})
+            subs.append(2)
+        if hyper:
+            for q in subs:
+                s.update({f"{p}hc{q}.in": (S,), f"{p}hc{q}.out": (S,), f"{p}hc{q}.mix": (S, S)})
+    return s
+
+
+def random_model(cfg: dict, seed: int, scale: float = 1.0, rel_rows=10) -> Dict[str, torch.Tensor]:
+    """weights whose every mechanism matters in the logits: matrices of unit-variance outputs, norm weights around one,
+    head and stream mixes far from the identity, biases and distance biases of order one"""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg, rel_rows).items():
+        leaf = name.rsplit(".", 1)[-1]
+        rnd = lambda: torch.randn(shape, generator=g)
+        if leaf in ("norm1", "norm2", "norm"):
+            t = 1.0 + 0.3 * rnd()
+        elif leaf == "talk":
+            t = torch.eye(shape[0]) + 0.4 * rnd()
+        elif leaf == "mix":
+            t = 0.8 * torch.eye(shape[0]) + 0.3 * rnd()
+        elif leaf in ("in", "out"):
+            t = 0.6 + 0.4 * rnd()
+        elif leaf == "temp":
+            t = 1.0 + 0.5 * rnd()
+        elif leaf == "rel":
+            t = 1.5 * rnd()
+        elif leaf == "b":
+            t = 0.5 * rnd()
+        elif leaf == "pos":
+            t = 0.7 * rnd()
+        elif leaf == "embed":
+            t = rnd()
+        else:
+            t = rnd() * (scale / math.sqrt(shape[-1]))
+        w[name] = t.to(torch.bfloat16)          # what a checkpoint stores
+    return w
