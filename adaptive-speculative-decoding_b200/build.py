@@ -29,7 +29,7 @@ COMPONENTS = {
     "mezilix": ["mezilix_engine.cu", "stream_ops.cu"],
     "rivetar": ["rivetar_engine.cu", "gla.cu", "window_attention.cu"],
     "mavipel": ["mavipel_engine.cu", "delta_rule.cu", "talking_attention.cu"],
-    "lukopel": ["lukopel_engine.cu", "residual_streams.cu", "mixed_attention.cu"],
+    "lukopel": ["lukopel_engine.cu", "residual_streams.cu", "mixed_attention.cu", "mixed_attention_tc.cu"],
     "qwen": ["engine.cu", "layers.cu", "attention.cu", "attention_tc.cu", "forward_persist.cu"],
     "sampling": ["api.cu", "sampler.cu", "stop_rule.cu"],
 }

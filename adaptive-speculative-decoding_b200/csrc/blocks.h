@@ -392,10 +392,14 @@ int launch_mix_post(const SeqIndex& ix, float* qkv, long long ld, const MixDims&
 // the error text
 int mix_attention_check(const MixDims& d, int talk);
 // Workspace: stats fp32 [2][shares][M][heads] (maximum and sum of every key share), part fp32 [shares][M][heads * dv].
+// scores fp32 [M][heads][keys] of steps of few tokens (optional).  mode 0: steps of few tokens and, in a bf16 engine,
+// prompts on the tensor cores take kernels of their own; 1: everything runs the general CUDA-core kernels.
 struct MixWork {
     float* stats = nullptr;
     float* part = nullptr;
-    long long stats_elems = 0, part_elems = 0;
+    float* scores = nullptr;
+    long long stats_elems = 0, part_elems = 0, score_elems = 0;
+    int mode = 0;
 };
 // out[m][h][:] (rows ldo apart, engine's element type) = sigmoid(gate[m][h]) * sum_j w'_h[j] v[j].  dist_bias fp32
 // [far + 1][heads]: the bias at distance min(i - j, far) (nullptr: none); talk fp32 [heads][heads] (nullptr: no mixing);

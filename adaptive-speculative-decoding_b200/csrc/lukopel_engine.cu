@@ -291,6 +291,8 @@ asd_lukopel_engine_t* asd_lukopel_create(const asd_lukopel_config* cfg, const as
     e->attn_ws.part_elems = (long long)(2048 * mixw);
     rc |= dev_alloc(e, &e->attn_ws.stats, (size_t)e->attn_ws.stats_elems);
     rc |= dev_alloc(e, &e->attn_ws.part, (size_t)e->attn_ws.part_elems);
+    e->attn_ws.score_elems = 8ll << 20;      // scores of steps of few tokens: tokens x heads x keys
+    rc |= dev_alloc(e, &e->attn_ws.scores, (size_t)e->attn_ws.score_elems);
     rc |= dev_alloc(e, &e->dev_error, 1);
     if (!rc && cudaMemset(e->dev_error, 0, sizeof(int)) != cudaSuccess) rc = -1;
     if (rc) {
@@ -359,6 +361,10 @@ int asd_lukopel_set_option(asd_lukopel_engine_t* h, const char* name, int value)
     if (!strcmp(name, "tc_min_rows")) {
         e->dn.tc_min_rows = value > 0 ? value : 1 << 30;
         e->dn.clear();
+        return 0;
+    }
+    if (!strcmp(name, "attn_general")) {
+        e->attn_ws.mode = value ? 1 : 0;
         return 0;
     }
     if (!strcmp(name, "profile")) {

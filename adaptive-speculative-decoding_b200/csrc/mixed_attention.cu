@@ -13,9 +13,12 @@
 #include <cuda_runtime.h>
 #include <math.h>
 
+#include <algorithm>
+
 #include "asd_internal.h"
 #include "blocks.h"
 #include "elem.cuh"
+#include "mixed_attention.h"
 
 namespace asd {
 
@@ -27,26 +30,6 @@ constexpr int NT = 256;         // threads: 16 row lanes (ty) x 16 key / column 
 constexpr int MAX_ROWS = 128;   // (head, query) pairs of a CTA
 constexpr int SLOTS = 8;        // result rows a thread accumulates (over all of the CTA's key/value groups)
 
-struct MixArgs {
-    SeqIndex ix;
-    const int* cu_q;
-    const int* seq_slot;
-    const float* q;
-    long long ldq;
-    MixDims d;
-    const float* dist_bias;
-    int far;
-    const float* talk;
-    const float* gate;
-    long long ldg;
-    PagedRows cache;
-    void* out;
-    int of32;
-    long long ldo;
-    float* stats;
-    float* part;
-    int QT, shares, gp, rag, dkp, dvp, vec;
-};
 
 struct Layout {
     int q, kv, p, w, talk, m, l, off, total;   // float offsets
@@ -371,6 +354,216 @@ __global__ void mix_merge_kernel(const float* part, int shares, int M, int H, in
     }
 }
 
+// ---------------------------------------------------------------------------------------------- steps of few tokens
+// Every token on its own (its position and slot), its keys cut into shares: grid (shares, tokens).  The scores are
+// computed once, by all threads over 64 keys x 4 heads at a time, and kept in the workspace (a few hundred KB per token
+// beside megabytes of cache rows); the second kernel reads them back, so keys are read once and values once.
+constexpr int DEC_OA = 8;   // heads of one key/value group a thread accumulates in the second kernel
+
+struct DecLayout {
+    int q, kv, p, w, os, talk, m, l, off, total;   // float offsets
+};
+__host__ __device__ inline DecLayout dec_layout(int H, int dkp, int dvp, bool apply, bool talk) {
+    DecLayout L;
+    int o = 0;
+    L.q = o, o += apply ? 0 : H * dkp;
+    L.kv = o, o += KT * (apply ? dvp : dkp + 4);
+    L.p = o, o += apply ? H * KT : 0;
+    L.w = o, o += (apply && talk) ? H * KT : 0;
+    L.os = o, o += apply ? H * dvp : 0;
+    L.talk = o, o += (apply && talk) ? H * H : 0;
+    L.m = o, o += apply ? H : 0;
+    L.l = o, o += apply ? H : 0;
+    o = (o + 3) & ~3;
+    L.off = o, o += 2 * KT;
+    L.total = o;
+    return L;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT) mix_dec_scores_kernel(MixArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, chunk = a.d.chunk;
+    const int m = blockIdx.y, share = blockIdx.x, M = a.ix.M;
+    const int dkp = a.dkp, KS = dkp + 4;
+    const DecLayout L = dec_layout(H, dkp, a.dvp, false, false);
+    float* qs = sm + L.q;
+    float* kv = sm + L.kv;
+    long long* rowoff = reinterpret_cast<long long*>(sm + L.off);
+    const int pos = a.ix.positions[m], slot = a.ix.token_slot[m];
+    const int kmin = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const int n = pos - kmin + 1, ntile = (n + KT - 1) / KT;
+    const int per = (ntile + a.shares - 1) / a.shares;
+    const int t0 = share * per, t1 = min(ntile, t0 + per);
+    const T* pool = static_cast<const T*>(a.cache.pool);
+    const int row_elems = G * (dk + dv), psz = a.cache.page_size;
+    float* srow = a.scores + (long long)m * H * a.score_ld;
+    for (int idx = tid; idx < H * dkp; idx += NT) {
+        const int h = idx / dkp, d = idx - h * dkp;
+        qs[idx] = d < dk ? a.q[(long long)m * a.ldq + (long long)h * dk + d] : 0.f;
+    }
+    const int key = tid & 63, hs = tid >> 6;
+    for (int t = t0; t < t1; ++t) {
+        const int kb = kmin + t * KT;
+        const int nk = min(KT, pos - kb + 1);
+        __syncthreads();
+        if (tid < KT) {
+            long long off = 0;
+            if (tid < nk) {
+                const int j = kb + tid;
+                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
+                off = ((long long)page * psz + j % psz) * row_elems;
+            }
+            rowoff[tid] = off;
+        }
+        for (int c = 0; c < G; ++c) {
+            __syncthreads();
+            load_tile<T>(pool, rowoff, nk, c * dk, dk, dkp, KS, kv, a.vec);
+            __syncthreads();
+            const float* kr = kv + (size_t)key * KS;
+            for (int hh = hs; hh < rep; hh += NT / KT) {
+                const int h = c * rep + hh;
+                const float* qr = qs + (size_t)h * dkp;
+                float acc = 0.f;
+                for (int d = 0; d < dkp; d += 4) {
+                    const float4 x = *reinterpret_cast<const float4*>(qr + d);
+                    const float4 y = *reinterpret_cast<const float4*>(kr + d);
+                    acc = fmaf(x.x, y.x, acc);
+                    acc = fmaf(x.y, y.y, acc);
+                    acc = fmaf(x.z, y.z, acc);
+                    acc = fmaf(x.w, y.w, acc);
+                }
+                if (key < nk) {
+                    float v = acc * a.d.scale;
+                    if (a.dist_bias) v += a.dist_bias[(long long)min(pos - (kb + key), a.far) * H + h];
+                    srow[(long long)h * a.score_ld + (kb - kmin) + key] = v;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // maximum and sum of exponentials of this share, head by head
+    const int k0 = min(n, t0 * KT), k1 = min(n, t1 * KT);
+    for (int h = warp; h < H; h += NT / 32) {
+        const float* r = srow + (long long)h * a.score_ld;
+        float mx = -INFINITY;
+        for (int j = k0 + lane; j < k1; j += 32) mx = fmaxf(mx, r[j]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int j = k0 + lane; j < k1; j += 32) sum += expf(r[j] - mx);
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            const long long at = (long long)m * H + h;
+            a.stats[(long long)share * M * H + at] = mx;
+            a.stats[(long long)(a.shares + share) * M * H + at] = k1 > k0 ? sum : 0.f;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT) mix_dec_apply_kernel(MixArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x;
+    const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, chunk = a.d.chunk;
+    const int m = blockIdx.y, share = blockIdx.x, M = a.ix.M;
+    const int dvp = a.dvp, CT = a.rag, nsub = NT / CT;
+    const bool talk = a.talk != nullptr;
+    const DecLayout L = dec_layout(H, a.dkp, dvp, true, talk);
+    float* kv = sm + L.kv;
+    float* Pm = sm + L.p;
+    float* Wm = talk ? sm + L.w : Pm;
+    float* os = sm + L.os;
+    float* talk_s = sm + L.talk;
+    float* Mh = sm + L.m;
+    float* Lh = sm + L.l;
+    long long* rowoff = reinterpret_cast<long long*>(sm + L.off);
+    const int pos = a.ix.positions[m], slot = a.ix.token_slot[m];
+    const int kmin = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const int n = pos - kmin + 1, ntile = (n + KT - 1) / KT;
+    const int per = (ntile + a.shares - 1) / a.shares;
+    const int t0 = share * per, t1 = min(ntile, t0 + per);
+    const T* pool = static_cast<const T*>(a.cache.pool);
+    const int row_elems = G * (dk + dv), psz = a.cache.page_size;
+    const float* srow = a.scores + (long long)m * H * a.score_ld;
+    if (talk)
+        for (int i = tid; i < H * H; i += NT) talk_s[i] = a.talk[i];
+    for (int i = tid; i < H * dvp; i += NT) os[i] = 0.f;
+    for (int h = tid; h < H; h += NT) {
+        const long long at = (long long)m * H + h;
+        float mm = -INFINITY, ll = 0.f;
+        for (int s = 0; s < a.shares; ++s) mm = fmaxf(mm, a.stats[(long long)s * M * H + at]);
+        for (int s = 0; s < a.shares; ++s) {
+            const float ms = a.stats[(long long)s * M * H + at];
+            if (ms > -INFINITY) ll += a.stats[(long long)(a.shares + s) * M * H + at] * expf(ms - mm);
+        }
+        Mh[h] = mm > -INFINITY ? mm : 0.f;
+        Lh[h] = ll > 0.f ? 1.f / ll : 0.f;
+    }
+    const int col = tid % CT, sub = tid / CT;
+    for (int t = t0; t < t1; ++t) {
+        const int kb = kmin + t * KT;
+        const int nk = min(KT, pos - kb + 1);
+        __syncthreads();
+        if (tid < KT) {
+            long long off = 0;
+            if (tid < nk) {
+                const int j = kb + tid;
+                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
+                off = ((long long)page * psz + j % psz) * row_elems;
+            }
+            rowoff[tid] = off;
+        }
+        for (int idx = tid; idx < H * KT; idx += NT) {
+            const int h = idx / KT, jj = idx - h * KT;
+            Pm[idx] = jj < nk ? expf(srow[(long long)h * a.score_ld + (kb - kmin) + jj] - Mh[h]) * Lh[h] : 0.f;
+        }
+        if (talk) {
+            __syncthreads();
+            for (int idx = tid; idx < H * KT; idx += NT) {
+                const int h = idx / KT, jj = idx - h * KT;
+                float acc = 0.f;
+                for (int g = 0; g < H; ++g) acc = fmaf(talk_s[h * H + g], Pm[g * KT + jj], acc);
+                Wm[idx] = acc;
+            }
+        }
+        for (int c = 0; c < G; ++c) {
+            __syncthreads();
+            load_tile<T>(pool, rowoff, nk, G * dk + c * dv, dv, dvp, dvp, kv, a.vec);
+            __syncthreads();
+            float acc[DEC_OA];
+#pragma unroll
+            for (int x = 0; x < DEC_OA; ++x) acc[x] = 0.f;
+            if (col < dvp) {
+                for (int jj = 0; jj < nk; ++jj) {
+                    const float v = kv[(size_t)jj * dvp + col];
+#pragma unroll
+                    for (int x = 0; x < DEC_OA; ++x) {
+                        const int hh = sub + nsub * x;
+                        if (hh < rep) acc[x] = fmaf(Wm[(c * rep + hh) * KT + jj], v, acc[x]);
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < DEC_OA; ++x) {
+                    const int hh = sub + nsub * x;
+                    if (hh < rep) os[(size_t)(c * rep + hh) * dvp + col] += acc[x];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < H * dv; idx += NT) {
+        const int h = idx / dv, c = idx - h * dv;
+        const float v = os[(size_t)h * dvp + c];
+        if (a.shares == 1) {
+            const float gate = a.gate ? 1.f / (1.f + expf(-a.gate[(long long)m * a.ldg + h])) : 1.f;
+            stx(a.out, (long long)m * a.ldo + idx, a.of32, v * gate);
+        } else {
+            a.part[((long long)share * M + m) * H * dv + idx] = v;
+        }
+    }
+}
+
 // dynamic shared memory: the row (n floats) + per-head sums of squares and factors
 template <typename T>
 __global__ void mix_post_kernel(SeqIndex ix, float* qkv, long long ld, MixDims d, MixPost p, PagedRows cache) {
@@ -453,6 +646,55 @@ int launch_mix_post(const SeqIndex& ix, float* qkv, long long ld, const MixDims&
     return 0;
 }
 
+int launch_mix_merge(const MixArgs& a, cudaStream_t stream) {
+    mix_merge_kernel<<<a.ix.M, 128, 0, stream>>>(a.part, a.shares, a.ix.M, a.d.heads, a.d.dv, a.gate, a.ldg, a.out, a.of32, a.ldo);
+    count_launch(1);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <typename T>
+static int launch_dec(const MixArgs& a, dim3 grid, size_t smem_scores, size_t smem_apply, cudaStream_t stream) {
+    static PerDeviceOnce once;
+    if (once.need()) {
+        ASD_CUDA(cudaFuncSetAttribute(mix_dec_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        ASD_CUDA(cudaFuncSetAttribute(mix_dec_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    }
+    mix_dec_scores_kernel<T><<<grid, NT, smem_scores, stream>>>(a);
+    mix_dec_apply_kernel<T><<<grid, NT, smem_apply, stream>>>(a);
+    count_launch(2);
+    ASD_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_mix_attention_decode(MixArgs a, int nseq, int max_kv_len, const MixWork& ws, cudaStream_t stream) {
+    (void)nseq;
+    const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, M = a.ix.M;
+    const int dkp = (a.d.dk + 3) & ~3, dvp = (a.d.dv + 3) & ~3;
+    const int CT = dvp <= 32 ? 32 : (dvp <= 64 ? 64 : 128);
+    if (dvp > 128 || rep > DEC_OA * (NT / CT) || !ws.scores || !ws.stats) return 1;
+    const long long score_ld = (max_kv_len + 3) & ~3;
+    if ((long long)M * H * score_ld > ws.score_elems) return 1;
+    const size_t sm_s = (size_t)dec_layout(H, dkp, dvp, false, false).total * sizeof(float);
+    const size_t sm_a = (size_t)dec_layout(H, dkp, dvp, true, a.talk != nullptr).total * sizeof(float);
+    if (sm_s > 200 * 1024 || sm_a > 200 * 1024) return 1;
+    const int key_tiles = (max_kv_len + KT - 1) / KT;
+    int shares = (int)std::min<long long>((444 + M - 1) / M, (long long)std::max(1, key_tiles / 2));
+    shares = std::max(1, std::min(shares, 32));
+    while (shares > 1 && (!ws.part || (long long)shares * M * H * a.d.dv > ws.part_elems ||
+                          (long long)2 * shares * M * H > ws.stats_elems))
+        --shares;
+    if ((long long)2 * shares * M * H > ws.stats_elems) return 1;
+    a.shares = shares, a.dkp = dkp, a.dvp = dvp, a.rag = CT, a.score_ld = score_ld, a.scores = ws.scores;
+    a.vec = (a.d.dk % 4 == 0 && a.d.dv % 4 == 0) ? 1 : 0;
+    const dim3 grid(shares, M);
+    const int rc = a.cache.f32 ? launch_dec<float>(a, grid, sm_s, sm_a, stream)
+                               : launch_dec<__nv_bfloat16>(a, grid, sm_s, sm_a, stream);
+    if (rc) return -1;
+    if (shares > 1 && launch_mix_merge(a, stream)) return -1;
+    return 0;
+}
+
 template <typename T, bool APPLY, int CB>
 static int launch_one(const MixArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     static PerDeviceOnce once;
@@ -485,8 +727,18 @@ int launch_mix_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slo
     MixArgs a;
     a.ix = ix, a.cu_q = cu_q, a.seq_slot = seq_slot, a.q = q, a.ldq = ldq, a.d = d, a.dist_bias = dist_bias, a.far = far;
     a.talk = talk, a.gate = gate, a.ldg = ldg, a.cache = cache, a.out = out, a.of32 = of32, a.ldo = ldo;
-    a.stats = ws.stats, a.part = ws.part, a.dkp = dkp, a.dvp = dvp;
+    a.stats = ws.stats, a.part = ws.part, a.dkp = dkp, a.dvp = dvp, a.scores = nullptr, a.score_ld = 0;
+    a.QT = 1, a.shares = 1, a.gp = 1, a.rag = 1;
     a.vec = (d.dk % 4 == 0 && d.dv % 4 == 0) ? 1 : 0;
+    // steps of few tokens; prompts of a bf16 engine on the tensor cores; else (and for sizes those refuse) the CUDA cores
+    if (max_qlen <= 4 && ws.mode != 1) {
+        const int rc = launch_mix_attention_decode(a, nseq, max_kv_len, ws, stream);
+        if (rc <= 0) return rc;
+    }
+    if (!cache.f32 && ws.mode != 1) {
+        const int rc = launch_mix_attention_tc(a, nseq, max_qlen, max_kv_len, ws, stream);
+        if (rc <= 0) return rc;
+    }
     // key/value groups per apply CTA and queries per tile: the CTA's (head, query) pairs, the result rows a thread
     // holds and shared memory must fit
     const int want_qt = max_qlen >= 16 ? 16 : (max_qlen >= 8 ? 8 : (max_qlen >= 4 ? 4 : (max_qlen >= 2 ? 2 : 1)));
@@ -535,9 +787,7 @@ int launch_mix_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slo
     }
     if (rc) return rc;
     if (shares > 1) {
-        mix_merge_kernel<<<ix.M, 128, 0, stream>>>(ws.part, shares, ix.M, H, d.dv, gate, ldg, out, of32, ldo);
-        count_launch(1);
-        ASD_CUDA(cudaGetLastError());
+        if (launch_mix_merge(a, stream)) return -1;
     }
     return 0;
 }

@@ -525,7 +525,9 @@ ASD_API size_t asd_lukopel_cache_bytes(const asd_lukopel_engine_t* e, int num_pa
 ASD_API size_t asd_lukopel_state_bytes(const asd_lukopel_engine_t* e, int max_seqs);   /* 0: the cache is all */
 ASD_API int asd_lukopel_set_cache(asd_lukopel_engine_t* e, void* pool, int num_pages, const int32_t* page_table,
                                   int max_seqs, int max_pages_per_seq, float* state);
-/* options: "tc_linear", "tc_min_rows" as for the Mezilix engine; "profile" */
+/* options: "tc_linear", "tc_min_rows" as for the Mezilix engine; "attn_general" (1: every attention runs the general
+ * CUDA-core kernels; 0, default: steps of few tokens and, in a bf16 engine, prompts on the tensor cores take kernels of
+ * their own where the sizes allow); "profile" */
 ASD_API int asd_lukopel_set_option(asd_lukopel_engine_t* e, const char* name, int value);
 /* Same arguments as asd_engine_forward (M <= max_tokens).  layer_out (optional, fp32 [runs][M][width]) receives the
  * sum of the streams that leaves every layer execution. */

@@ -485,6 +485,29 @@ def test_single_token_steps_with_key_shares_over_several_ctas():
         close(eng)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_general_and_special_attention_kernels_agree(dtype):
+    """prompts of a bf16 engine run on the tensor cores and steps of few tokens keep their scores between two kernels;
+    option attn_general sends everything through the general CUDA-core kernels instead: same logits"""
+    cfg = config([full(heads=8, kv_heads=2, dim=32, vdim=32, bias_max=70, mlp=dense(64)),
+                  chunked(heads=4, kv_heads=4, dim=24, vdim=40, size=37, mlp=dense(64)),
+                  full(heads=6, kv_heads=3, dim=20, vdim=12, bias_max=30), chunked(heads=6, kv_heads=2, dim=16, vdim=64, size=100)],
+                 max_positions=400)
+    w = O.random_model(cfg, seed=47, rel_rows=[12, 0, 8, 0])
+    ids = tokens(260, 120, 48)
+    ref = oracle(cfg, w, ids)
+    outs = []
+    for general in (0, 1):
+        eng = make_engine(cfg, w, dtype=dtype, max_tokens=256)
+        eng.set_option("attn_general", general)
+        slot = eng.open_sequence()
+        outs.append(feed(eng, slot, ids, [200, 30, 9, 3, 2, 1, 1, 4, 1]))
+        close(eng)
+    for got in outs:
+        assert (rel_err(got, ref)[1] < 2e-4) if dtype == torch.float32 else (rel_err(got, ref)[0] < 5e-2)
+    assert rel_err(outs[0], outs[1].double().cpu())[1] < (2e-4 if dtype == torch.float32 else 0.1)
+
+
 # ------------------------------------------------------------------------------------------------ other sizes
 def random_config(seed):
     g = torch.Generator().manual_seed(1000 + seed)
