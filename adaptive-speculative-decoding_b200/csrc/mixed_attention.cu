@@ -51,33 +51,45 @@ __host__ __device__ inline Layout mix_layout(int rows, int dkp, int dvp, int hea
     return L;
 }
 
-// cache rows [kb, kb + nk) of one key/value head -> dst[key][np] fp32 (zeros beyond n and beyond nk)
+// cache rows [kb, kb + nk) of one key/value head -> dst[key][np] fp32 (zeros beyond n and beyond nk).  A thread issues
+// the loads of eight pieces before it converts and stores any of them, so that they are in flight together.
 template <typename T>
 __device__ __forceinline__ void load_tile(const T* pool, const long long* rowoff, int nk, int head_off, int n, int np,
                                           int stride, float* dst, int vec) {
-    const int n4 = np >> 2;
-    for (int idx = threadIdx.x; idx < KT * n4; idx += NT) {
-        const int key = idx / n4, d = (idx - key * n4) << 2;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (key < nk) {
+    constexpr int U = 8;
+    const int n4 = np >> 2, total = KT * n4;
+    for (int base = threadIdx.x; base < total; base += NT * U) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * NT;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (idx >= total) continue;
+            const int key = idx / n4, d = (idx - key * n4) << 2;
+            if (key >= nk) continue;
             const T* src = pool + rowoff[key] + head_off + d;
             if (vec) {
                 if constexpr (sizeof(T) == 2) {
                     const uint2 raw = *reinterpret_cast<const uint2*>(src);
-                    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-                    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-                    v = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+                    v[u] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
                 } else {
-                    v = *reinterpret_cast<const float4*>(src);
+                    v[u] = *reinterpret_cast<const float4*>(src);
                 }
             } else {
-                if (d + 0 < n) v.x = ldf(src + 0);
-                if (d + 1 < n) v.y = ldf(src + 1);
-                if (d + 2 < n) v.z = ldf(src + 2);
-                if (d + 3 < n) v.w = ldf(src + 3);
+                if (d + 0 < n) v[u].x = ldf(src + 0);
+                if (d + 1 < n) v[u].y = ldf(src + 1);
+                if (d + 2 < n) v[u].z = ldf(src + 2);
+                if (d + 3 < n) v[u].w = ldf(src + 3);
             }
         }
-        *reinterpret_cast<float4*>(dst + (size_t)key * stride + d) = v;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * NT;
+            if (idx >= total) continue;
+            const int key = idx / n4, d = (idx - key * n4) << 2;
+            *reinterpret_cast<float4*>(dst + (size_t)key * stride + d) = v[u];
+        }
     }
 }
 
@@ -345,13 +357,14 @@ __global__ void __launch_bounds__(NT) mix_attn_kernel(MixArgs a) {
 __global__ void mix_merge_kernel(const float* part, int shares, int M, int H, int dv, const float* gate, long long ldg,
                                  void* out, int of32, long long ldo) {
     const int m = blockIdx.x, n = H * dv;
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < shares; ++s) acc += part[((long long)s * M + m) * n + e];
-        const int h = e / dv;
-        if (gate) acc *= 1.f / (1.f + expf(-gate[(long long)m * ldg + h]));
-        stx(out, (long long)m * ldo + e, of32, acc);
-    }
+    const int e = blockIdx.y * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < shares; ++s) acc += part[((long long)s * M + m) * n + e];
+    const int h = e / dv;
+    if (gate) acc *= 1.f / (1.f + expf(-gate[(long long)m * ldg + h]));
+    stx(out, (long long)m * ldo + e, of32, acc);
 }
 
 // ---------------------------------------------------------------------------------------------- steps of few tokens
@@ -363,14 +376,15 @@ constexpr int DEC_OA = 8;   // heads of one key/value group a thread accumulates
 struct DecLayout {
     int q, kv, p, w, os, talk, m, l, off, total;   // float offsets
 };
-__host__ __device__ inline DecLayout dec_layout(int H, int dkp, int dvp, bool apply, bool talk) {
+// sk: keys a share holds at most (second kernel)
+__host__ __device__ inline DecLayout dec_layout(int H, int dkp, int dvp, bool apply, bool talk, int sk) {
     DecLayout L;
     int o = 0;
     L.q = o, o += apply ? 0 : H * dkp;
     L.kv = o, o += KT * (apply ? dvp : dkp + 4);
-    L.p = o, o += apply ? H * KT : 0;
-    L.w = o, o += (apply && talk) ? H * KT : 0;
-    L.os = o, o += apply ? H * dvp : 0;
+    L.p = o, o += (apply && talk) ? H * KT : 0;
+    L.w = o, o += apply ? H * sk : 0;
+    L.os = o, o += apply ? (NT / 32) * DEC_OA * dvp : 0;     // the warps' sums of one key/value group
     L.talk = o, o += (apply && talk) ? H * H : 0;
     L.m = o, o += apply ? H : 0;
     L.l = o, o += apply ? H : 0;
@@ -387,7 +401,7 @@ __global__ void __launch_bounds__(NT) mix_dec_scores_kernel(MixArgs a) {
     const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, chunk = a.d.chunk;
     const int m = blockIdx.y, share = blockIdx.x, M = a.ix.M;
     const int dkp = a.dkp, KS = dkp + 4;
-    const DecLayout L = dec_layout(H, dkp, a.dvp, false, false);
+    const DecLayout L = dec_layout(H, dkp, a.dvp, false, false, 0);
     float* qs = sm + L.q;
     float* kv = sm + L.kv;
     long long* rowoff = reinterpret_cast<long long*>(sm + L.off);
@@ -461,19 +475,22 @@ __global__ void __launch_bounds__(NT) mix_dec_scores_kernel(MixArgs a) {
     }
 }
 
+// Second kernel: the share's normalised, mixed weights for ALL its keys first (shared memory, [heads][keys of the share]),
+// then one key/value group after the other: a warp takes every eighth key of a value tile, a lane four value columns,
+// so a value is read once for all heads of its group; the warps' sums are added in index order.
 template <typename T>
 __global__ void __launch_bounds__(NT) mix_dec_apply_kernel(MixArgs a) {
     extern __shared__ __align__(16) float sm[];
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, chunk = a.d.chunk;
     const int m = blockIdx.y, share = blockIdx.x, M = a.ix.M;
-    const int dvp = a.dvp, CT = a.rag, nsub = NT / CT;
+    const int dvp = a.dvp, SK = a.rag;       // keys a share holds at most (a multiple of the tile)
     const bool talk = a.talk != nullptr;
-    const DecLayout L = dec_layout(H, a.dkp, dvp, true, talk);
+    const DecLayout L = dec_layout(H, a.dkp, dvp, true, talk, SK);
     float* kv = sm + L.kv;
     float* Pm = sm + L.p;
-    float* Wm = talk ? sm + L.w : Pm;
-    float* os = sm + L.os;
+    float* Wm = sm + L.w;
+    float* red = sm + L.os;
     float* talk_s = sm + L.talk;
     float* Mh = sm + L.m;
     float* Lh = sm + L.l;
@@ -488,7 +505,6 @@ __global__ void __launch_bounds__(NT) mix_dec_apply_kernel(MixArgs a) {
     const float* srow = a.scores + (long long)m * H * a.score_ld;
     if (talk)
         for (int i = tid; i < H * H; i += NT) talk_s[i] = a.talk[i];
-    for (int i = tid; i < H * dvp; i += NT) os[i] = 0.f;
     for (int h = tid; h < H; h += NT) {
         const long long at = (long long)m * H + h;
         float mm = -INFINITY, ll = 0.f;
@@ -500,23 +516,17 @@ __global__ void __launch_bounds__(NT) mix_dec_apply_kernel(MixArgs a) {
         Mh[h] = mm > -INFINITY ? mm : 0.f;
         Lh[h] = ll > 0.f ? 1.f / ll : 0.f;
     }
-    const int col = tid % CT, sub = tid / CT;
+    // weights of the share's keys
     for (int t = t0; t < t1; ++t) {
         const int kb = kmin + t * KT;
         const int nk = min(KT, pos - kb + 1);
         __syncthreads();
-        if (tid < KT) {
-            long long off = 0;
-            if (tid < nk) {
-                const int j = kb + tid;
-                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
-                off = ((long long)page * psz + j % psz) * row_elems;
-            }
-            rowoff[tid] = off;
-        }
+        float* dstp = talk ? Pm : Wm + (t - t0) * KT;
+        const int ldp = talk ? KT : SK;
+#pragma unroll 4
         for (int idx = tid; idx < H * KT; idx += NT) {
             const int h = idx / KT, jj = idx - h * KT;
-            Pm[idx] = jj < nk ? expf(srow[(long long)h * a.score_ld + (kb - kmin) + jj] - Mh[h]) * Lh[h] : 0.f;
+            dstp[h * ldp + jj] = jj < nk ? expf(srow[(long long)h * a.score_ld + (kb - kmin) + jj] - Mh[h]) * Lh[h] : 0.f;
         }
         if (talk) {
             __syncthreads();
@@ -524,42 +534,70 @@ __global__ void __launch_bounds__(NT) mix_dec_apply_kernel(MixArgs a) {
                 const int h = idx / KT, jj = idx - h * KT;
                 float acc = 0.f;
                 for (int g = 0; g < H; ++g) acc = fmaf(talk_s[h * H + g], Pm[g * KT + jj], acc);
-                Wm[idx] = acc;
-            }
-        }
-        for (int c = 0; c < G; ++c) {
-            __syncthreads();
-            load_tile<T>(pool, rowoff, nk, G * dk + c * dv, dv, dvp, dvp, kv, a.vec);
-            __syncthreads();
-            float acc[DEC_OA];
-#pragma unroll
-            for (int x = 0; x < DEC_OA; ++x) acc[x] = 0.f;
-            if (col < dvp) {
-                for (int jj = 0; jj < nk; ++jj) {
-                    const float v = kv[(size_t)jj * dvp + col];
-#pragma unroll
-                    for (int x = 0; x < DEC_OA; ++x) {
-                        const int hh = sub + nsub * x;
-                        if (hh < rep) acc[x] = fmaf(Wm[(c * rep + hh) * KT + jj], v, acc[x]);
-                    }
-                }
-#pragma unroll
-                for (int x = 0; x < DEC_OA; ++x) {
-                    const int hh = sub + nsub * x;
-                    if (hh < rep) os[(size_t)(c * rep + hh) * dvp + col] += acc[x];
-                }
+                Wm[h * SK + (t - t0) * KT + jj] = acc;
             }
         }
     }
-    __syncthreads();
-    for (int idx = tid; idx < H * dv; idx += NT) {
-        const int h = idx / dv, c = idx - h * dv;
-        const float v = os[(size_t)h * dvp + c];
-        if (a.shares == 1) {
-            const float gate = a.gate ? 1.f / (1.f + expf(-a.gate[(long long)m * a.ldg + h])) : 1.f;
-            stx(a.out, (long long)m * a.ldo + idx, a.of32, v * gate);
-        } else {
-            a.part[((long long)share * M + m) * H * dv + idx] = v;
+    const bool col_ok = 4 * lane < dvp;
+    for (int c = 0; c < G; ++c) {
+        float acc[DEC_OA][4];
+#pragma unroll
+        for (int x = 0; x < DEC_OA; ++x)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[x][e] = 0.f;
+        for (int t = t0; t < t1; ++t) {
+            const int kb = kmin + t * KT;
+            const int nk = min(KT, pos - kb + 1);
+            __syncthreads();
+            if (tid < KT) {
+                long long off = 0;
+                if (tid < nk) {
+                    const int j = kb + tid;
+                    const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
+                    off = ((long long)page * psz + j % psz) * row_elems;
+                }
+                rowoff[tid] = off;
+            }
+            __syncthreads();
+            load_tile<T>(pool, rowoff, nk, G * dk + c * dv, dv, dvp, dvp, kv, a.vec);
+            __syncthreads();
+            if (col_ok) {
+                const float* wbase = Wm + (size_t)(c * rep) * SK + (t - t0) * KT;
+                for (int jj = warp; jj < nk; jj += NT / 32) {
+                    const float4 v = *reinterpret_cast<const float4*>(kv + (size_t)jj * dvp + 4 * lane);
+#pragma unroll
+                    for (int x = 0; x < DEC_OA; ++x) {
+                        if (x >= rep) break;
+                        const float w = wbase[(size_t)x * SK + jj];
+                        acc[x][0] = fmaf(w, v.x, acc[x][0]);
+                        acc[x][1] = fmaf(w, v.y, acc[x][1]);
+                        acc[x][2] = fmaf(w, v.z, acc[x][2]);
+                        acc[x][3] = fmaf(w, v.w, acc[x][3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (col_ok) {
+#pragma unroll
+            for (int x = 0; x < DEC_OA; ++x) {
+                if (x >= rep) break;
+                *reinterpret_cast<float4*>(red + ((size_t)warp * rep + x) * dvp + 4 * lane) =
+                    make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < rep * dv; idx += NT) {
+            const int x = idx / dv, col = idx - x * dv, h = c * rep + x;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < NT / 32; ++w) v += red[((size_t)w * rep + x) * dvp + col];
+            if (a.shares == 1) {
+                const float gate = a.gate ? 1.f / (1.f + expf(-a.gate[(long long)m * a.ldg + h])) : 1.f;
+                stx(a.out, (long long)m * a.ldo + (long long)h * dv + col, a.of32, v * gate);
+            } else {
+                a.part[((long long)share * M + m) * H * dv + (long long)h * dv + col] = v;
+            }
         }
     }
 }
@@ -647,7 +685,8 @@ int launch_mix_post(const SeqIndex& ix, float* qkv, long long ld, const MixDims&
 }
 
 int launch_mix_merge(const MixArgs& a, cudaStream_t stream) {
-    mix_merge_kernel<<<a.ix.M, 128, 0, stream>>>(a.part, a.shares, a.ix.M, a.d.heads, a.d.dv, a.gate, a.ldg, a.out, a.of32, a.ldo);
+    const dim3 grid(a.ix.M, (a.d.heads * a.d.dv + 255) / 256);
+    mix_merge_kernel<<<grid, 256, 0, stream>>>(a.part, a.shares, a.ix.M, a.d.heads, a.d.dv, a.gate, a.ldg, a.out, a.of32, a.ldo);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
@@ -671,21 +710,25 @@ int launch_mix_attention_decode(MixArgs a, int nseq, int max_kv_len, const MixWo
     (void)nseq;
     const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, M = a.ix.M;
     const int dkp = (a.d.dk + 3) & ~3, dvp = (a.d.dv + 3) & ~3;
-    const int CT = dvp <= 32 ? 32 : (dvp <= 64 ? 64 : 128);
-    if (dvp > 128 || rep > DEC_OA * (NT / CT) || !ws.scores || !ws.stats) return 1;
+    if (dvp > 128 || rep > DEC_OA || !ws.scores || !ws.stats) return 1;
     const long long score_ld = (max_kv_len + 3) & ~3;
     if ((long long)M * H * score_ld > ws.score_elems) return 1;
-    const size_t sm_s = (size_t)dec_layout(H, dkp, dvp, false, false).total * sizeof(float);
-    const size_t sm_a = (size_t)dec_layout(H, dkp, dvp, true, a.talk != nullptr).total * sizeof(float);
-    if (sm_s > 200 * 1024 || sm_a > 200 * 1024) return 1;
     const int key_tiles = (max_kv_len + KT - 1) / KT;
     int shares = (int)std::min<long long>((444 + M - 1) / M, (long long)std::max(1, key_tiles / 2));
     shares = std::max(1, std::min(shares, 32));
-    while (shares > 1 && (!ws.part || (long long)shares * M * H * a.d.dv > ws.part_elems ||
-                          (long long)2 * shares * M * H > ws.stats_elems))
-        --shares;
+    // the second kernel keeps the weights of a share's keys in shared memory: more shares where they would not fit
+    auto smem_apply = [&](int sh) {
+        const int per = (key_tiles + sh - 1) / sh;
+        return (size_t)dec_layout(H, dkp, dvp, true, a.talk != nullptr, per * KT).total * sizeof(float);
+    };
+    while (smem_apply(shares) > 160 * 1024 && shares < 64 && shares < key_tiles) ++shares;
+    const size_t sm_s = (size_t)dec_layout(H, dkp, dvp, false, false, 0).total * sizeof(float);
+    const size_t sm_a = smem_apply(shares);
+    if (sm_s > 200 * 1024 || sm_a > 200 * 1024) return 1;
+    if (shares > 1 && (!ws.part || (long long)shares * M * H * a.d.dv > ws.part_elems)) return 1;
     if ((long long)2 * shares * M * H > ws.stats_elems) return 1;
-    a.shares = shares, a.dkp = dkp, a.dvp = dvp, a.rag = CT, a.score_ld = score_ld, a.scores = ws.scores;
+    a.shares = shares, a.dkp = dkp, a.dvp = dvp, a.rag = ((key_tiles + shares - 1) / shares) * KT, a.score_ld = score_ld;
+    a.scores = ws.scores;
     a.vec = (a.d.dk % 4 == 0 && a.d.dv % 4 == 0) ? 1 : 0;
     const dim3 grid(shares, M);
     const int rc = a.cache.f32 ? launch_dec<float>(a, grid, sm_s, sm_a, stream)

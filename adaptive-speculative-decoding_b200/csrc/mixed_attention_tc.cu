@@ -51,22 +51,35 @@ __host__ __device__ inline TcLayout tc_layout(int rows, int DS, int VS, int ng, 
 template <int KT>
 __device__ __forceinline__ void stage_rows(const bf16* pool, const long long* rowoff, int nk, int head_off, int hstep, int ng,
                                            int n, int np, int stride, bf16* dst, int vec) {
-    const int n8 = np >> 3;
-    for (int idx = threadIdx.x; idx < ng * KT * n8; idx += NT) {
-        const int d = (idx % n8) << 3, rk = idx / n8, key = rk % KT, cl = rk / KT;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (key < nk) {
+    constexpr int U = 8;   // loads a thread has in flight before it stores any
+    const int n8 = np >> 3, total = ng * KT * n8;
+    for (int base = threadIdx.x; base < total; base += NT * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * NT;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx >= total) continue;
+            const int d = (idx % n8) << 3, rk = idx / n8, key = rk % KT, cl = rk / KT;
+            if (key >= nk) continue;
             const bf16* src = pool + rowoff[key] + head_off + cl * hstep + d;
             if (vec && d + 8 <= n) {
-                v = *reinterpret_cast<const uint4*>(src);
+                v[u] = *reinterpret_cast<const uint4*>(src);
             } else {
-                bf16 tmp[8];
+                unsigned short tmp[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) tmp[e] = d + e < n ? src[e] : __float2bfloat16(0.f);
-                v = *reinterpret_cast<const uint4*>(tmp);
+                for (int e = 0; e < 8; ++e) tmp[e] = d + e < n ? __bfloat16_as_ushort(src[e]) : (unsigned short)0;
+                v[u] = make_uint4(tmp[0] | ((uint32_t)tmp[1] << 16), tmp[2] | ((uint32_t)tmp[3] << 16),
+                                  tmp[4] | ((uint32_t)tmp[5] << 16), tmp[6] | ((uint32_t)tmp[7] << 16));
             }
         }
-        *reinterpret_cast<uint4*>(dst + ((size_t)cl * KT + key) * stride + d) = v;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * NT;
+            if (idx >= total) continue;
+            const int d = (idx % n8) << 3, rk = idx / n8, key = rk % KT, cl = rk / KT;
+            *reinterpret_cast<uint4*>(dst + ((size_t)cl * KT + key) * stride + d) = v[u];
+        }
     }
 }
 
