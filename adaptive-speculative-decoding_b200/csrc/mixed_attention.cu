@@ -381,7 +381,7 @@ __host__ __device__ inline DecLayout dec_layout(int H, int dkp, int dvp, bool ap
     DecLayout L;
     int o = 0;
     L.q = o, o += apply ? 0 : H * dkp;
-    L.kv = o, o += KT * (apply ? dvp : dkp + 4);
+    L.kv = o;                                            // (no tile is staged)
     L.p = o, o += (apply && talk) ? H * KT : 0;
     L.w = o, o += apply ? H * sk : 0;
     L.os = o, o += apply ? (NT / 32) * DEC_OA * dvp : 0;     // the warps' sums of one key/value group
@@ -389,76 +389,116 @@ __host__ __device__ inline DecLayout dec_layout(int H, int dkp, int dvp, bool ap
     L.m = o, o += apply ? H : 0;
     L.l = o, o += apply ? H : 0;
     o = (o + 3) & ~3;
-    L.off = o, o += 2 * KT;
+    L.off = o, o += 2 * (sk > KT ? sk : KT);   // 64-bit row offsets of the share's keys
     L.total = o;
     return L;
 }
 
+// eight consecutive elements of a cache row as floats (vec: one 16-byte load, or two for fp32 rows; else element by
+// element with zeros from n on)
+template <typename T>
+__device__ __forceinline__ void load8(const T* src, int d, int n, int vec, float (&v)[8]) {
+    if (vec && d + 8 <= n) {
+        if constexpr (sizeof(T) == 2) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src);
+            v[0] = __uint_as_float(raw.x << 16), v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16), v[3] = __uint_as_float(raw.y & 0xffff0000u);
+            v[4] = __uint_as_float(raw.z << 16), v[5] = __uint_as_float(raw.z & 0xffff0000u);
+            v[6] = __uint_as_float(raw.w << 16), v[7] = __uint_as_float(raw.w & 0xffff0000u);
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = d + e < n ? ldf(src + e) : 0.f;
+    }
+}
+
+// cache row offsets of the share's keys [k0, k1) (relative to kmin) into rowoff[0 .. k1 - k0)
+__device__ __forceinline__ void share_rows(const MixArgs& a, int slot, int kmin, int k0, int k1, int row_elems, long long* rowoff) {
+    const int psz = a.cache.page_size;
+    for (int i = threadIdx.x; i < k1 - k0; i += NT) {
+        const int j = kmin + k0 + i;
+        const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
+        rowoff[i] = ((long long)page * psz + j % psz) * row_elems;
+    }
+}
+
+// First kernel.  Nothing is staged: eight lanes share a key row (16-byte pieces, whole lines per warp), a warp four
+// keys at a time, against the queries of the key's group in shared memory; the partial dot products of the group's heads
+// are closed by shuffles.
 template <typename T>
 __global__ void __launch_bounds__(NT) mix_dec_scores_kernel(MixArgs a) {
     extern __shared__ __align__(16) float sm[];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, l8 = lane & 7, sub = lane >> 3;
     const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, chunk = a.d.chunk;
     const int m = blockIdx.y, share = blockIdx.x, M = a.ix.M;
-    const int dkp = a.dkp, KS = dkp + 4;
-    const DecLayout L = dec_layout(H, dkp, a.dvp, false, false, 0);
+    const int dkp = a.dkp, SK = a.rag;
+    const DecLayout L = dec_layout(H, dkp, a.dvp, false, false, SK);
     float* qs = sm + L.q;
-    float* kv = sm + L.kv;
     long long* rowoff = reinterpret_cast<long long*>(sm + L.off);
     const int pos = a.ix.positions[m], slot = a.ix.token_slot[m];
     const int kmin = chunk > 0 ? (pos / chunk) * chunk : 0;
     const int n = pos - kmin + 1, ntile = (n + KT - 1) / KT;
     const int per = (ntile + a.shares - 1) / a.shares;
-    const int t0 = share * per, t1 = min(ntile, t0 + per);
+    const int k0 = min(n, share * per * KT), k1 = min(n, (share + 1) * per * KT);
     const T* pool = static_cast<const T*>(a.cache.pool);
-    const int row_elems = G * (dk + dv), psz = a.cache.page_size;
+    const int row_elems = G * (dk + dv);
     float* srow = a.scores + (long long)m * H * a.score_ld;
     for (int idx = tid; idx < H * dkp; idx += NT) {
         const int h = idx / dkp, d = idx - h * dkp;
         qs[idx] = d < dk ? a.q[(long long)m * a.ldq + (long long)h * dk + d] : 0.f;
     }
-    const int key = tid & 63, hs = tid >> 6;
-    for (int t = t0; t < t1; ++t) {
-        const int kb = kmin + t * KT;
-        const int nk = min(KT, pos - kb + 1);
-        __syncthreads();
-        if (tid < KT) {
-            long long off = 0;
-            if (tid < nk) {
-                const int j = kb + tid;
-                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
-                off = ((long long)page * psz + j % psz) * row_elems;
-            }
-            rowoff[tid] = off;
-        }
-        for (int c = 0; c < G; ++c) {
-            __syncthreads();
-            load_tile<T>(pool, rowoff, nk, c * dk, dk, dkp, KS, kv, a.vec);
-            __syncthreads();
-            const float* kr = kv + (size_t)key * KS;
-            for (int hh = hs; hh < rep; hh += NT / KT) {
-                const int h = c * rep + hh;
-                const float* qr = qs + (size_t)h * dkp;
-                float acc = 0.f;
-                for (int d = 0; d < dkp; d += 4) {
-                    const float4 x = *reinterpret_cast<const float4*>(qr + d);
-                    const float4 y = *reinterpret_cast<const float4*>(kr + d);
-                    acc = fmaf(x.x, y.x, acc);
-                    acc = fmaf(x.y, y.y, acc);
-                    acc = fmaf(x.z, y.z, acc);
-                    acc = fmaf(x.w, y.w, acc);
+    share_rows(a, slot, kmin, k0, k1, row_elems, rowoff);
+    __syncthreads();
+    const int npiece = dkp >> 3, nkey = k1 - k0;
+    for (int c = 0; c < G; ++c) {
+        const float* qg = qs + (size_t)c * rep * dkp;
+#pragma unroll 2
+        for (int kq = warp * 4; kq < nkey; kq += (NT / 32) * 4) {
+            const int ki = kq + sub;
+            const bool live = ki < nkey;
+            const T* kr = pool + rowoff[live ? ki : 0] + c * dk;
+            float acc[DEC_OA];
+#pragma unroll
+            for (int x = 0; x < DEC_OA; ++x) acc[x] = 0.f;
+            for (int p = l8; p < npiece; p += 8) {
+                float kk[8];
+                load8<T>(kr + 8 * p, 8 * p, dk, a.gp, kk);
+#pragma unroll
+                for (int x = 0; x < DEC_OA; ++x) {
+                    if (x >= rep) break;
+                    const float4 q0 = *reinterpret_cast<const float4*>(qg + (size_t)x * dkp + 8 * p);
+                    const float4 q1 = *reinterpret_cast<const float4*>(qg + (size_t)x * dkp + 8 * p + 4);
+                    acc[x] = fmaf(q0.x, kk[0], acc[x]);
+                    acc[x] = fmaf(q0.y, kk[1], acc[x]);
+                    acc[x] = fmaf(q0.z, kk[2], acc[x]);
+                    acc[x] = fmaf(q0.w, kk[3], acc[x]);
+                    acc[x] = fmaf(q1.x, kk[4], acc[x]);
+                    acc[x] = fmaf(q1.y, kk[5], acc[x]);
+                    acc[x] = fmaf(q1.z, kk[6], acc[x]);
+                    acc[x] = fmaf(q1.w, kk[7], acc[x]);
                 }
-                if (key < nk) {
-                    float v = acc * a.d.scale;
-                    if (a.dist_bias) v += a.dist_bias[(long long)min(pos - (kb + key), a.far) * H + h];
-                    srow[(long long)h * a.score_ld + (kb - kmin) + key] = v;
+            }
+#pragma unroll
+            for (int x = 0; x < DEC_OA; ++x) {
+                if (x >= rep) break;
+                float v = acc[x];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (l8 == 0 && live) {
+                    const int h = c * rep + x;
+                    v *= a.d.scale;
+                    if (a.dist_bias) v += a.dist_bias[(long long)min(pos - (kmin + k0 + ki), a.far) * H + h];
+                    srow[(long long)h * a.score_ld + k0 + ki] = v;
                 }
             }
         }
     }
     __syncthreads();
     // maximum and sum of exponentials of this share, head by head
-    const int k0 = min(n, t0 * KT), k1 = min(n, t1 * KT);
     for (int h = warp; h < H; h += NT / 32) {
         const float* r = srow + (long long)h * a.score_ld;
         float mx = -INFINITY;
@@ -539,40 +579,54 @@ __global__ void __launch_bounds__(NT) mix_dec_apply_kernel(MixArgs a) {
         }
     }
     const bool col_ok = 4 * lane < dvp;
+    const int k0 = min(n, t0 * KT), k1 = min(n, t1 * KT), nkey = k1 - k0;
+    __syncthreads();
+    share_rows(a, slot, kmin, k0, k1, row_elems, rowoff);
+    __syncthreads();
     for (int c = 0; c < G; ++c) {
         float acc[DEC_OA][4];
 #pragma unroll
         for (int x = 0; x < DEC_OA; ++x)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[x][e] = 0.f;
-        for (int t = t0; t < t1; ++t) {
-            const int kb = kmin + t * KT;
-            const int nk = min(KT, pos - kb + 1);
-            __syncthreads();
-            if (tid < KT) {
-                long long off = 0;
-                if (tid < nk) {
-                    const int j = kb + tid;
-                    const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
-                    off = ((long long)page * psz + j % psz) * row_elems;
+        if (col_ok) {   // nothing staged: a warp reads a key's value row (four columns a lane), every eighth key
+            const float* wbase = Wm + (size_t)(c * rep) * SK;
+            const int voff = G * dk + c * dv + 4 * lane;
+            for (int kb = warp; kb < nkey; kb += (NT / 32) * 4) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int ki = kb + u * (NT / 32);
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (ki >= nkey) continue;
+                    const T* src = pool + rowoff[ki] + voff;
+                    if (a.vec) {
+                        if constexpr (sizeof(T) == 2) {
+                            const uint2 raw = *reinterpret_cast<const uint2*>(src);
+                            v[u] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                               __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                        } else {
+                            v[u] = *reinterpret_cast<const float4*>(src);
+                        }
+                    } else {
+                        if (4 * lane + 0 < dv) v[u].x = ldf(src + 0);
+                        if (4 * lane + 1 < dv) v[u].y = ldf(src + 1);
+                        if (4 * lane + 2 < dv) v[u].z = ldf(src + 2);
+                        if (4 * lane + 3 < dv) v[u].w = ldf(src + 3);
+                    }
                 }
-                rowoff[tid] = off;
-            }
-            __syncthreads();
-            load_tile<T>(pool, rowoff, nk, G * dk + c * dv, dv, dvp, dvp, kv, a.vec);
-            __syncthreads();
-            if (col_ok) {
-                const float* wbase = Wm + (size_t)(c * rep) * SK + (t - t0) * KT;
-                for (int jj = warp; jj < nk; jj += NT / 32) {
-                    const float4 v = *reinterpret_cast<const float4*>(kv + (size_t)jj * dvp + 4 * lane);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int ki = kb + u * (NT / 32);
+                    if (ki >= nkey) continue;
 #pragma unroll
                     for (int x = 0; x < DEC_OA; ++x) {
                         if (x >= rep) break;
-                        const float w = wbase[(size_t)x * SK + jj];
-                        acc[x][0] = fmaf(w, v.x, acc[x][0]);
-                        acc[x][1] = fmaf(w, v.y, acc[x][1]);
-                        acc[x][2] = fmaf(w, v.z, acc[x][2]);
-                        acc[x][3] = fmaf(w, v.w, acc[x][3]);
+                        const float w = wbase[(size_t)x * SK + ki];
+                        acc[x][0] = fmaf(w, v[u].x, acc[x][0]);
+                        acc[x][1] = fmaf(w, v[u].y, acc[x][1]);
+                        acc[x][2] = fmaf(w, v[u].z, acc[x][2]);
+                        acc[x][3] = fmaf(w, v[u].w, acc[x][3]);
                     }
                 }
             }
@@ -709,7 +763,7 @@ static int launch_dec(const MixArgs& a, dim3 grid, size_t smem_scores, size_t sm
 int launch_mix_attention_decode(MixArgs a, int nseq, int max_kv_len, const MixWork& ws, cudaStream_t stream) {
     (void)nseq;
     const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, M = a.ix.M;
-    const int dkp = (a.d.dk + 3) & ~3, dvp = (a.d.dv + 3) & ~3;
+    const int dkp = (a.d.dk + 7) & ~7, dvp = (a.d.dv + 3) & ~3;
     if (dvp > 128 || rep > DEC_OA || !ws.scores || !ws.stats) return 1;
     const long long score_ld = (max_kv_len + 3) & ~3;
     if ((long long)M * H * score_ld > ws.score_elems) return 1;
@@ -722,14 +776,16 @@ int launch_mix_attention_decode(MixArgs a, int nseq, int max_kv_len, const MixWo
         return (size_t)dec_layout(H, dkp, dvp, true, a.talk != nullptr, per * KT).total * sizeof(float);
     };
     while (smem_apply(shares) > 160 * 1024 && shares < 64 && shares < key_tiles) ++shares;
-    const size_t sm_s = (size_t)dec_layout(H, dkp, dvp, false, false, 0).total * sizeof(float);
+    const size_t sm_s = (size_t)dec_layout(H, dkp, dvp, false, false, ((key_tiles + shares - 1) / shares) * KT).total * sizeof(float);
     const size_t sm_a = smem_apply(shares);
     if (sm_s > 200 * 1024 || sm_a > 200 * 1024) return 1;
     if (shares > 1 && (!ws.part || (long long)shares * M * H * a.d.dv > ws.part_elems)) return 1;
     if ((long long)2 * shares * M * H > ws.stats_elems) return 1;
     a.shares = shares, a.dkp = dkp, a.dvp = dvp, a.rag = ((key_tiles + shares - 1) / shares) * KT, a.score_ld = score_ld;
     a.scores = ws.scores;
-    a.vec = (a.d.dk % 4 == 0 && a.d.dv % 4 == 0) ? 1 : 0;
+    a.vec = (a.d.dk % 4 == 0 && a.d.dv % 4 == 0) ? 1 : 0;                       // a lane's four value columns in one load
+    const int piece = a.cache.f32 ? 4 : 8;                                       // elements of a 16-byte load
+    a.gp = (a.d.dk % piece == 0 && a.d.dv % piece == 0) ? 1 : 0;                 // a lane's eight key elements in 16-byte loads
     const dim3 grid(shares, M);
     const int rc = a.cache.f32 ? launch_dec<float>(a, grid, sm_s, sm_a, stream)
                                : launch_dec<__nv_bfloat16>(a, grid, sm_s, sm_a, stream);
