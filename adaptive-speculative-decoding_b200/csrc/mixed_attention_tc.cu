@@ -30,60 +30,49 @@ struct TcLayout {
     int qh, ql, kv, p, talk, m, l, off, total;   // byte offsets, multiples of 16
 };
 __host__ __device__ inline int up16(int x) { return (x + 15) & ~15; }
-__host__ __device__ inline TcLayout tc_layout(int rows, int DS, int VS, int ng, int KT, int heads, bool apply, bool talk) {
+__host__ __device__ inline TcLayout tc_layout(int rows, int DS, int VS, int ng, int KT, int heads, bool apply, bool talk,
+                                              int nbuf) {
     TcLayout L;
     int o = 0;
     L.qh = o, o += rows * DS * 2;
     L.ql = o, o += rows * DS * 2;
     const int kvw = DS > VS ? DS : VS;
-    L.kv = o, o += ng * KT * kvw * 2;
+    L.kv = o, o += nbuf * ng * KT * kvw * 2;
     L.p = o, o += (apply && talk) ? rows * (KT + 8) * 4 : 0;
     L.talk = o, o += (apply && talk) ? up16(heads * heads * 4) : 0;
     L.m = o, o += apply ? up16(rows * 4) : 0;
     L.l = o, o += apply ? up16(rows * 4) : 0;
-    L.off = o, o += KT * 8;
+    L.off = o, o += 2 * KT * 8;
     L.total = o;
     return L;
 }
 
 // cache rows of the tile's keys, `ng` key/value heads from head_off on (n elements each, hstep apart), -> dst[(group *
 // KT + key) * stride + d] for d < np (zeros beyond n and beyond nk)
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// vec: every 16-byte piece of a row is aligned and whole, so the copies are cp.async (zero-filled beyond the row and
+// beyond nk) that the caller commits and waits for; else plain loads and stores, done when the call returns.
 template <int KT>
 __device__ __forceinline__ void stage_rows(const bf16* pool, const long long* rowoff, int nk, int head_off, int hstep, int ng,
                                            int n, int np, int stride, bf16* dst, int vec) {
-    constexpr int U = 8;   // loads a thread has in flight before it stores any
     const int n8 = np >> 3, total = ng * KT * n8;
-    for (int base = threadIdx.x; base < total; base += NT * U) {
-        uint4 v[U];
+    for (int idx = threadIdx.x; idx < total; idx += NT) {
+        const int d = (idx % n8) << 3, rk = idx / n8, key = rk % KT, cl = rk / KT;
+        bf16* to = dst + ((size_t)cl * KT + key) * stride + d;
+        const bool live = key < nk && d < n;
+        const bf16* src = pool + (live ? rowoff[key] + head_off + cl * hstep + d : 0);
+        if (vec) {
+            cp_async16(smem_addr(to), src, live);
+        } else {
+            unsigned short tmp[8];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int idx = base + u * NT;
-            v[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (idx >= total) continue;
-            const int d = (idx % n8) << 3, rk = idx / n8, key = rk % KT, cl = rk / KT;
-            if (key >= nk) continue;
-            const bf16* src = pool + rowoff[key] + head_off + cl * hstep + d;
-            if (vec && d + 8 <= n) {
-                v[u] = *reinterpret_cast<const uint4*>(src);
-            } else {
-                unsigned short tmp[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) tmp[e] = d + e < n ? __bfloat16_as_ushort(src[e]) : (unsigned short)0;
-                v[u] = make_uint4(tmp[0] | ((uint32_t)tmp[1] << 16), tmp[2] | ((uint32_t)tmp[3] << 16),
-                                  tmp[4] | ((uint32_t)tmp[5] << 16), tmp[6] | ((uint32_t)tmp[7] << 16));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int idx = base + u * NT;
-            if (idx >= total) continue;
-            const int d = (idx % n8) << 3, rk = idx / n8, key = rk % KT, cl = rk / KT;
-            *reinterpret_cast<uint4*>(dst + ((size_t)cl * KT + key) * stride + d) = v[u];
+            for (int e = 0; e < 8; ++e) tmp[e] = (live && d + e < n) ? __bfloat16_as_ushort(src[e]) : (unsigned short)0;
+            *reinterpret_cast<uint4*>(to) = make_uint4(tmp[0] | ((uint32_t)tmp[1] << 16), tmp[2] | ((uint32_t)tmp[3] << 16),
+                                                       tmp[4] | ((uint32_t)tmp[5] << 16), tmp[6] | ((uint32_t)tmp[7] << 16));
         }
     }
 }
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 template <int KT, int NDV, bool APPLY, bool TALK>
 __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
@@ -100,10 +89,12 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
     const int hbeg = gc0 * rep, rows = ng * rep * QT;
     const int dkp = a.dkp, DS = dkp + 8, VS = NDV * 8 + 8, kvw = DS > VS ? DS : VS;
     constexpr int PSF = KT + 8;
-    const TcLayout L = tc_layout(a.gp * rep * QT, DS, VS, a.gp, KT, H, APPLY, TALK);
+    const int pipe = a.rag;      // 1: two tile buffers, copies run behind the products; 0: one buffer, copy then compute
+    const TcLayout L = tc_layout(a.gp * rep * QT, DS, VS, a.gp, KT, H, APPLY, TALK, pipe ? 2 : 1);
     bf16* Qh = reinterpret_cast<bf16*>(smraw + L.qh);
     bf16* Ql = reinterpret_cast<bf16*>(smraw + L.ql);
     bf16* kvb = reinterpret_cast<bf16*>(smraw + L.kv);
+    bf16* kvb2 = kvb + (pipe ? (size_t)a.gp * KT * kvw : 0);
     float* Pm = reinterpret_cast<float*>(smraw + L.p);
     float* talk_s = reinterpret_cast<float*>(smraw + L.talk);
     float* Mr = reinterpret_cast<float*>(smraw + L.m);
@@ -146,7 +137,24 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
             Lr[row] = ll > 0.f ? 1.f / ll : 0.f;
         }
     }
+    auto tile_rows = [&](int tl, long long* ro) {     // cache row offsets of tile tl's keys (threads below KT)
+        if (tid < KT) {
+            const int j = kmin + tl * KT + tid;
+            long long off = 0;
+            if (j <= p1) {
+                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
+                off = ((long long)page * psz + j % psz) * row_elems;
+            }
+            ro[tid] = off;
+        }
+    };
+    if (pipe && t0 < t1) tile_rows(t0, rowoff + (t0 & 1) * KT);
     __syncthreads();
+    if (pipe && t0 < t1) {
+        stage_rows<KT>(pool, rowoff + (t0 & 1) * KT, min(KT, p1 - (kmin + t0 * KT) + 1), gc0 * dk, dk, ng, dk, dkp, kvw,
+                       APPLY ? kvb : ((t0 & 1) ? kvb2 : kvb), a.vec);
+        cp_async_commit();
+    }
 
     const int rb = warp * 16;
     const bool active = rb < rows;
@@ -174,26 +182,39 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
     for (int tl = t0; tl < t1; ++tl) {
         const int kb = kmin + tl * KT;
         const int nk = min(KT, p1 - kb + 1);
-        __syncthreads();
-        if (tid < KT) {
-            long long off = 0;
-            if (tid < nk) {
-                const int j = kb + tid;
-                const int page = a.cache.page_table[(long long)slot * a.cache.max_pages + j / psz];
-                off = ((long long)page * psz + j % psz) * row_elems;
-            }
-            rowoff[tid] = off;
+        const long long* ro = rowoff + (pipe ? (tl & 1) * KT : 0);
+        bf16* kcur = (!APPLY && pipe && (tl & 1)) ? kvb2 : kvb;
+        bf16* vcur = kvb2;
+        const bool more = tl + 1 < t1;
+        const int nk_next = min(KT, p1 - (kb + KT) + 1);
+        if (pipe) {
+            if (more) tile_rows(tl + 1, rowoff + ((tl + 1) & 1) * KT);
+        } else {
+            __syncthreads();
+            tile_rows(tl, rowoff);
+            __syncthreads();
+            stage_rows<KT>(pool, ro, nk, gc0 * dk, dk, ng, dk, dkp, kvw, kcur, a.vec);
+            cp_async_commit();
         }
-        __syncthreads();
-        stage_rows<KT>(pool, rowoff, nk, gc0 * dk, dk, ng, dk, dkp, kvw, kvb, a.vec);
-        __syncthreads();
+        cp_async_wait<0>();
+        __syncthreads();   // this tile's keys are here; every warp is done with the tile before
+        if (pipe) {        // behind the score products: this tile's values (second pass) or the next tile's keys (first)
+            if (APPLY) {
+                stage_rows<KT>(pool, ro, nk, G * dk + gc0 * dv, dv, ng, dv, NDV * 8, kvw, vcur, a.vec);
+                cp_async_commit();
+            } else if (more) {
+                stage_rows<KT>(pool, rowoff + ((tl + 1) & 1) * KT, nk_next, gc0 * dk, dk, ng, dk, dkp, kvw,
+                               ((tl + 1) & 1) ? kvb2 : kvb, a.vec);
+                cp_async_commit();
+            }
+        }
         float s[KT / 8][4];
 #pragma unroll
         for (int n = 0; n < KT / 8; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
         if (active) {
-            const bf16* kt = kvb + (size_t)cw * KT * kvw;
+            const bf16* kt = kcur + (size_t)cw * KT * kvw;
             const uint32_t qh_addr = smem_addr(Qh + (size_t)(rb + lr + (mat & 1) * 8) * DS + (mat >> 1) * 8);
             const uint32_t ql_addr = smem_addr(Ql + (size_t)(rb + lr + (mat & 1) * 8) * DS + (mat >> 1) * 8);
             const uint32_t k_addr = smem_addr(kt + (size_t)(lr + (mat >> 1) * 8) * kvw + (mat & 1) * 8);
@@ -260,7 +281,15 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
         }
         if (!APPLY) continue;
         __syncthreads();   // every warp has read its keys; the weights of all heads are in shared memory
-        stage_rows<KT>(pool, rowoff, nk, G * dk + gc0 * dv, dv, ng, dv, NDV * 8, kvw, kvb, a.vec);
+        if (pipe) {        // behind the mix and the value products: the next tile's keys
+            if (more) {
+                stage_rows<KT>(pool, rowoff + ((tl + 1) & 1) * KT, nk_next, gc0 * dk, dk, ng, dk, dkp, kvw, kvb, a.vec);
+                cp_async_commit();
+            }
+        } else {
+            stage_rows<KT>(pool, ro, nk, G * dk + gc0 * dv, dv, ng, dv, NDV * 8, kvw, vcur, a.vec);
+            cp_async_commit();
+        }
         if (TALK && active) {   // w'_h = sum_g talk[h][g] w_g, straight into this warp's fragment registers
 #pragma unroll
             for (int n = 0; n < KT / 8; ++n)
@@ -281,9 +310,13 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
                 }
             }
         }
+        if (pipe && more)
+            cp_async_wait<1>();     // the values; the next tile's keys stay in flight
+        else
+            cp_async_wait<0>();
         __syncthreads();
         if (active) {
-            const bf16* vt = kvb + (size_t)cw * KT * kvw;
+            const bf16* vt = vcur + (size_t)cw * KT * kvw;
             const uint32_t v_addr = smem_addr(vt + (size_t)(lr + (mat & 1) * 8) * kvw + (mat >> 1) * 8);
 #pragma unroll
             for (int j = 0; j < KT / 16; ++j) {
@@ -368,7 +401,7 @@ int launch_mix_attention_tc(MixArgs a, int nseq, int max_qlen, int max_kv_len, c
     const int dkp = (dk + 15) & ~15, DS = dkp + 8, VS = ndv * 8 + 8;
     // queries per tile and key/value groups per CTA: rows = groups * rep * QT <= 128, a multiple of 16, and every block of
     // 16 rows inside one key/value group
-    int QT = 0, gp = 0, KT = 0;
+    int QT = 0, gp = 0, KT = 0, pipe = 0;
     size_t smem_apply = 0;
     for (int qt = 32; qt >= 2 && !QT; qt >>= 1) {
         if (qt > 16 && max_qlen < 24) continue;
@@ -376,16 +409,19 @@ int launch_mix_attention_tc(MixArgs a, int nseq, int max_qlen, int max_kv_len, c
         const int g = talk ? G : std::min(G, 128 / std::max(1, rep * qt));
         if (g < 1 || g * rep * qt > 128 || (g * rep * qt) % 16) continue;
         if (!(qt % 16 == 0 || (16 % qt == 0 && rep % (16 / qt) == 0))) continue;
-        for (int kt : {64, 32}) {
-            const size_t sm = (size_t)tc_layout(g * rep * qt, DS, VS, g, kt, H, true, talk).total;
-            if (sm <= 200 * 1024) {
-                QT = qt, gp = g, KT = kt, smem_apply = sm;
-                break;
+        for (int nbuf : {2, 1}) {
+            for (int kt : {64, 32}) {
+                const size_t sm = (size_t)tc_layout(g * rep * qt, DS, VS, g, kt, H, true, talk, nbuf).total;
+                if (sm <= 200 * 1024) {
+                    QT = qt, gp = g, KT = kt, smem_apply = sm, pipe = nbuf == 2;
+                    break;
+                }
             }
+            if (QT) break;
         }
     }
     if (!QT) return 1;
-    a.QT = QT, a.gp = gp, a.dkp = dkp, a.dvp = ndv * 8;
+    a.QT = QT, a.gp = gp, a.dkp = dkp, a.dvp = ndv * 8, a.rag = pipe;
     a.vec = (dk % 8 == 0 && dv % 8 == 0) ? 1 : 0;
     const int tiles = (max_qlen + QT - 1) / QT, ngroups = (G + gp - 1) / gp;
     int shares = 1;
@@ -400,7 +436,7 @@ int launch_mix_attention_tc(MixArgs a, int nseq, int max_qlen, int max_kv_len, c
     }
     if (!ws.stats || (long long)2 * shares * a.ix.M * H > ws.stats_elems) return 1;
     a.shares = shares;
-    const size_t smem_stats = (size_t)tc_layout(gp * rep * QT, DS, VS, gp, KT, H, false, false).total;
+    const size_t smem_stats = (size_t)tc_layout(gp * rep * QT, DS, VS, gp, KT, H, false, false, pipe ? 2 : 1).total;
     const dim3 grid(tiles, nseq, shares * ngroups);
     int rc;
     if (KT == 64) {
