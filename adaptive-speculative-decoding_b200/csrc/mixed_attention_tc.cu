@@ -81,7 +81,8 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
     const int H = a.d.heads, G = a.d.kv_heads, rep = H / G, dk = a.d.dk, dv = a.d.dv, QT = a.QT, chunk = a.d.chunk;
     const int b = blockIdx.y;
     const int seq_end = a.cu_q[b + 1];
-    const int q_beg = a.cu_q[b] + blockIdx.x * QT;
+    // the last query tiles of a prompt see the most keys: they start first
+    const int q_beg = a.cu_q[b] + (int)(gridDim.x - 1 - blockIdx.x) * QT;
     if (q_beg >= seq_end) return;
     const int nq = min(QT, seq_end - q_beg);
     const int share = blockIdx.z % a.shares, gsel = blockIdx.z / a.shares;
@@ -227,8 +228,8 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
                     uint32_t bq[4];
                     ldsm_x4(k_addr + (n2 * 16 * kvw + ks) * 2, bq);
                     mma_bf16(s[2 * n2], ah, bq[0], bq[1]);
-                    mma_bf16(s[2 * n2], al, bq[0], bq[1]);
                     mma_bf16(s[2 * n2 + 1], ah, bq[2], bq[3]);
+                    mma_bf16(s[2 * n2], al, bq[0], bq[1]);
                     mma_bf16(s[2 * n2 + 1], al, bq[2], bq[3]);
                 }
             }
@@ -333,8 +334,8 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
                     uint32_t bv[4];
                     ldsm_x4_t(v_addr + (j * 16 * kvw + n * 8) * 2, bv);
                     mma_bf16(O[n], ph, bv[0], bv[1]);
-                    mma_bf16(O[n], pl, bv[0], bv[1]);
                     mma_bf16(O[n + 1], ph, bv[2], bv[3]);
+                    mma_bf16(O[n], pl, bv[0], bv[1]);
                     mma_bf16(O[n + 1], pl, bv[2], bv[3]);
                 }
             }
