@@ -74,7 +74,9 @@ __device__ __forceinline__ void stage_rows(const bf16* pool, const long long* ro
     }
 }
 
-template <int KT, int NDV, bool APPLY, bool TALK>
+// ONE (second pass without a head mix, all keys in one share): no first pass at all; the running maximum rescales the
+// sums tile by tile and the division by the softmax sum comes last.
+template <int KT, int NDV, bool APPLY, bool TALK, bool ONE>
 __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -120,7 +122,7 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
         Qh[(size_t)row * DS + d] = hi;
         Ql[(size_t)row * DS + d] = __float2bfloat16(v - __bfloat162float(hi));
     }
-    if (APPLY) {
+    if (APPLY && !ONE) {
         if (TALK)
             for (int i = tid; i < H * H; i += NT) talk_s[i] = a.talk[i];
         for (int row = tid; row < rows; row += NT) {   // final statistics: the key shares' maxima and sums merged
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
         posx[x] = p0 + ix_[x];
         lox[x] = chunk > 0 ? (posx[x] / chunk) * chunk : 0;
         okx[x] = active && ix_[x] < nq;
-        if (APPLY && active) Mx[x] = Mr[r], iLx[x] = Lr[r];
+        if (APPLY && !ONE && active) Mx[x] = Mr[r], iLx[x] = Lr[r];
     }
     const int cw = active ? (hbeg + rb / QT) / rep - gc0 : 0;   // the warp's key/value group among the CTA's
     float mrun[2] = {-INFINITY, -INFINITY}, lrun[2] = {0.f, 0.f};
@@ -243,7 +245,7 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
                     float v = s[n][e] * a.d.scale;
                     if (a.dist_bias && ok) v += a.dist_bias[(long long)min(posx[x] - j, a.far) * H + hx[x]];
                     v = ok ? v : -INFINITY;
-                    if (!APPLY) {
+                    if (!APPLY || ONE) {
                         s[n][e] = v;
                         tmax[x] = fmaxf(tmax[x], v);
                     } else {
@@ -271,6 +273,26 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
                         lrun[x] = lrun[x] * keep + sum;
                         mrun[x] = mnew;
                     }
+                }
+            } else if (ONE) {
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    tmax[x] = fmaxf(tmax[x], __shfl_xor_sync(0xffffffffu, tmax[x], 1));
+                    tmax[x] = fmaxf(tmax[x], __shfl_xor_sync(0xffffffffu, tmax[x], 2));
+                    const float mnew = fmaxf(mrun[x], tmax[x]);
+                    const float keep = (mrun[x] > -INFINITY && mnew > -INFINITY) ? expf(mrun[x] - mnew) : 0.f;
+                    float sum = 0.f;      // this thread's part of the row's sum; the quad's parts are added at the end
+#pragma unroll
+                    for (int n = 0; n < KT / 8; ++n) {
+                        const float w0 = s[n][2 * x] > -INFINITY ? expf(s[n][2 * x] - mnew) : 0.f;
+                        const float w1 = s[n][2 * x + 1] > -INFINITY ? expf(s[n][2 * x + 1] - mnew) : 0.f;
+                        s[n][2 * x] = w0, s[n][2 * x + 1] = w1;
+                        sum += w0 + w1;
+                    }
+                    lrun[x] = lrun[x] * keep + sum;
+                    mrun[x] = mnew;
+#pragma unroll
+                    for (int n = 0; n < NDV; ++n) O[n][2 * x] *= keep, O[n][2 * x + 1] *= keep;
                 }
             } else if (TALK) {
 #pragma unroll
@@ -355,6 +377,17 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
         }
         return;
     }
+    if (ONE) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            float l = lrun[x];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+            for (int n = 0; n < NDV; ++n) O[n][2 * x] *= inv, O[n][2 * x + 1] *= inv;
+        }
+    }
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         if (!okx[x]) continue;
@@ -376,20 +409,31 @@ __global__ void __launch_bounds__(NT) mix_tc_kernel(MixArgs a) {
     }
 }
 
-template <int KT, int NDV, bool APPLY, bool TALK>
+template <int KT, int NDV, bool APPLY, bool TALK, bool ONE>
 int launch_tc(const MixArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
     static PerDeviceOnce once;
     if (once.need())
-        ASD_CUDA(cudaFuncSetAttribute(mix_tc_kernel<KT, NDV, APPLY, TALK>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    mix_tc_kernel<KT, NDV, APPLY, TALK><<<grid, NT, smem, stream>>>(a);
+        ASD_CUDA(cudaFuncSetAttribute(mix_tc_kernel<KT, NDV, APPLY, TALK, ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      220 * 1024));
+    mix_tc_kernel<KT, NDV, APPLY, TALK, ONE><<<grid, NT, smem, stream>>>(a);
     count_launch(1);
     ASD_CUDA(cudaGetLastError());
     return 0;
 }
 
 template <int KT, int NDV>
-int launch_apply(const MixArgs& a, dim3 grid, size_t smem, cudaStream_t stream) {
-    return a.talk ? launch_tc<KT, NDV, true, true>(a, grid, smem, stream) : launch_tc<KT, NDV, true, false>(a, grid, smem, stream);
+int launch_apply(const MixArgs& a, bool one, dim3 grid, size_t smem, cudaStream_t stream) {
+    if (a.talk) return launch_tc<KT, NDV, true, true, false>(a, grid, smem, stream);
+    return one ? launch_tc<KT, NDV, true, false, true>(a, grid, smem, stream)
+               : launch_tc<KT, NDV, true, false, false>(a, grid, smem, stream);
+}
+
+template <int KT>
+int launch_passes(const MixArgs& a, bool one, int ndv, dim3 grid, size_t smem_stats, size_t smem_apply, cudaStream_t stream) {
+    if (!one && launch_tc<KT, 4, false, false, false>(a, grid, smem_stats, stream)) return -1;
+    return ndv == 4 ? launch_apply<KT, 4>(a, one, grid, smem_apply, stream)
+                    : (ndv == 8 ? launch_apply<KT, 8>(a, one, grid, smem_apply, stream)
+                                : launch_apply<KT, 16>(a, one, grid, smem_apply, stream));
 }
 
 }  // namespace
@@ -439,18 +483,9 @@ int launch_mix_attention_tc(MixArgs a, int nseq, int max_qlen, int max_kv_len, c
     a.shares = shares;
     const size_t smem_stats = (size_t)tc_layout(gp * rep * QT, DS, VS, gp, KT, H, false, false, pipe ? 2 : 1).total;
     const dim3 grid(tiles, nseq, shares * ngroups);
-    int rc;
-    if (KT == 64) {
-        rc = launch_tc<64, 4, false, false>(a, grid, smem_stats, stream);
-        if (!rc)
-            rc = ndv == 4 ? launch_apply<64, 4>(a, grid, smem_apply, stream)
-                          : (ndv == 8 ? launch_apply<64, 8>(a, grid, smem_apply, stream) : launch_apply<64, 16>(a, grid, smem_apply, stream));
-    } else {
-        rc = launch_tc<32, 4, false, false>(a, grid, smem_stats, stream);
-        if (!rc)
-            rc = ndv == 4 ? launch_apply<32, 4>(a, grid, smem_apply, stream)
-                          : (ndv == 8 ? launch_apply<32, 8>(a, grid, smem_apply, stream) : launch_apply<32, 16>(a, grid, smem_apply, stream));
-    }
+    const bool one = !talk && shares == 1;      // no mix across heads and one share: one pass with a running maximum
+    const int rc = KT == 64 ? launch_passes<64>(a, one, ndv, grid, smem_stats, smem_apply, stream)
+                            : launch_passes<32>(a, one, ndv, grid, smem_stats, smem_apply, stream);
     if (rc) return -1;
     if (shares > 1 && launch_mix_merge(a, stream)) return -1;
     return 0;
