@@ -388,7 +388,7 @@ struct MixPost {
 };
 int launch_mix_post(const SeqIndex& ix, float* qkv, long long ld, const MixDims& d, const MixPost& p,
                     const PagedRows& cache, cudaStream_t stream);
-// 0 if the kernels take these sizes (dv <= 128, dk <= 512, at most 64 heads when the weights are mixed), else -1 and
+// 0 if the kernels take these sizes (dv <= 256, dk <= 512, at most 128 heads when the weights are mixed), else -1 and
 // the error text
 int mix_attention_check(const MixDims& d, int talk);
 // Workspace: stats fp32 [2][shares][M][heads] (maximum and sum of every key share), part fp32 [shares][M][heads * dv].

@@ -391,7 +391,6 @@ int asd_lukopel_forward(asd_lukopel_engine_t* h, const int32_t* tokens, const in
         if (ly.c.ff_kind) need.insert(need.end(), {"norm2", "w_up", "w_down"});
         for (const char* n : need)
             if (!ly.w(n)) return set_error("asd_lukopel_forward: layer %d has no tensor %s", (int)l, n);
-        if (ly.w("talk") && ly.c.heads > 64) return set_error("asd_lukopel_forward: layer %d mixes more than 64 heads", (int)l);
     }
     if (!tokens || !positions || !token_slot || !cu_q || !seq_slot || nseq <= 0 || max_qlen <= 0)
         return set_error("asd_lukopel_forward: bad index arguments");

@@ -289,14 +289,12 @@ __global__ void __launch_bounds__(NT) mix_attn_kernel(MixArgs a) {
                 active[s] = (s / a.rag == cl) && rg < Rg;
                 wrow[s] = Wm + (size_t)(lrow0 + (active[s] ? rg : 0)) * PS;
             }
-            const bool col1 = CB > 1 && (64 + tx * 4) < dvp;
-            const bool col0 = tx * 4 < dvp;
             for (int j = 0; j < nk; ++j) {
                 float4 v[CB];
-                v[0] = col0 ? *reinterpret_cast<const float4*>(kv + (size_t)j * dvp + tx * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                if (CB > 1)
-                    v[CB - 1] = col1 ? *reinterpret_cast<const float4*>(kv + (size_t)j * dvp + 64 + tx * 4)
-                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+                    v[cb] = (cb * 64 + tx * 4) < dvp ? *reinterpret_cast<const float4*>(kv + (size_t)j * dvp + cb * 64 + tx * 4)
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int s = 0; s < SLOTS; ++s) {
                     if (!active[s]) continue;
@@ -808,10 +806,10 @@ static int launch_one(const MixArgs& a, dim3 grid, size_t smem, cudaStream_t str
 int mix_attention_check(const MixDims& d, int talk) {
     if (d.heads <= 0 || d.kv_heads <= 0 || d.heads % d.kv_heads || d.dk <= 0 || d.dv <= 0 || d.chunk < 0)
         return set_error("mixed attention: bad sizes");
-    if (d.dv > 128) return set_error("mixed attention: value size %d above 128", d.dv);
+    if (d.dv > 256) return set_error("mixed attention: value size %d above 256", d.dv);
     if (d.dk > 512) return set_error("mixed attention: key size %d above 512", d.dk);
     if (d.heads / d.kv_heads > MAX_ROWS) return set_error("mixed attention: more than %d query heads per key head", MAX_ROWS);
-    if (talk && d.heads > 64) return set_error("mixed attention: more than 64 heads with mixed weights");
+    if (talk && d.heads > MAX_ROWS) return set_error("mixed attention: more than %d heads with mixed weights", MAX_ROWS);
     return 0;
 }
 
@@ -873,16 +871,20 @@ int launch_mix_attention(const SeqIndex& ix, const int* cu_q, const int* seq_slo
     a.shares = shares;
     const size_t smem_stats = (size_t)mix_layout(rep * QT, dkp, dvp, H, false, false).total * sizeof(float);
     const dim3 gs(tiles, nseq, shares * G), ga(tiles, nseq, shares * ngroups);
-    const bool wide = dvp > 64;
+    const int cb = dvp <= 64 ? 1 : (dvp <= 128 ? 2 : 4);
     int rc;
     if (cache.f32) {
         rc = launch_one<float, false, 1>(a, gs, smem_stats, stream);
-        if (!rc) rc = wide ? launch_one<float, true, 2>(a, ga, smem_apply, stream) : launch_one<float, true, 1>(a, ga, smem_apply, stream);
+        if (!rc)
+            rc = cb == 1 ? launch_one<float, true, 1>(a, ga, smem_apply, stream)
+                         : (cb == 2 ? launch_one<float, true, 2>(a, ga, smem_apply, stream)
+                                    : launch_one<float, true, 4>(a, ga, smem_apply, stream));
     } else {
         rc = launch_one<__nv_bfloat16, false, 1>(a, gs, smem_stats, stream);
         if (!rc)
-            rc = wide ? launch_one<__nv_bfloat16, true, 2>(a, ga, smem_apply, stream)
-                      : launch_one<__nv_bfloat16, true, 1>(a, ga, smem_apply, stream);
+            rc = cb == 1 ? launch_one<__nv_bfloat16, true, 1>(a, ga, smem_apply, stream)
+                         : (cb == 2 ? launch_one<__nv_bfloat16, true, 2>(a, ga, smem_apply, stream)
+                                    : launch_one<__nv_bfloat16, true, 4>(a, ga, smem_apply, stream));
     }
     if (rc) return rc;
     if (shares > 1) {

@@ -243,14 +243,16 @@ def test_chunked_attention_alone_every_step_matters():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
 def test_many_heads_large_heads_and_sizes_that_divide_nothing(dtype):
-    """twenty mixed heads, sixteen key/value heads (an apply CTA then multiplies the values of a part of them), value
-    heads of 128 and 100, keys of 136 and of 7, one query head per key head and forty per key head"""
+    """twenty and eighty mixed heads, sixteen key/value heads (an apply CTA then multiplies the values of a part of them),
+    value heads of 100, 128, 200 and 256, keys of 136 and of 7, one query head per key head and forty per key head"""
     cfg = config([full(heads=20, kv_heads=4, dim=16, vdim=16, bias_max=30),
                   full(heads=16, kv_heads=16, dim=8, vdim=12, bias_max=12),
                   chunked(heads=2, kv_heads=1, dim=136, vdim=128, size=50, scale=0.05),
                   full(heads=3, kv_heads=1, dim=7, vdim=100, bias_max=64, scale=0.4),
-                  chunked(heads=40, kv_heads=1, dim=12, vdim=5, size=23)])
-    w = O.random_model(cfg, seed=15, rel_rows=[12, 6, 0, 20, 0])
+                  chunked(heads=40, kv_heads=1, dim=12, vdim=5, size=23),
+                  full(heads=80, kv_heads=10, dim=8, vdim=4, bias_max=20), chunked(heads=2, kv_heads=2, dim=16, vdim=200, size=31),
+                  full(heads=2, kv_heads=1, dim=12, vdim=256, bias_max=50)])
+    w = O.random_model(cfg, seed=15, rel_rows=[12, 6, 0, 20, 0, 8, 0, 4])
     ids = tokens(80, 120, 16)
     ref = oracle(cfg, w, ids)
     for cuts in ([80], [60] + [1] * 20, [7] * 12):
